@@ -1,0 +1,317 @@
+// C ABI (include/tvdcn_b200.h): validation, engine choice, workspace layout, kernel sequencing.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/tvdcn_b200.h"
+#include "kernels.h"
+#include "plan.h"
+
+namespace tvdcn_b200 {
+
+static std::atomic<uint64_t> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+    return fail(TVDCN_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+static int64_t prod(const int64_t *v, int n) {
+    int64_t r = 1;
+    for (int i = 0; i < n; ++i) r *= v[i];
+    return r;
+}
+
+int check_problem(const tvdcn_problem *p) {
+    if (p == nullptr) return fail(TVDCN_ERR_INVALID, "problem is NULL");
+    if (p->dim < 1 || p->dim > 3) return fail(TVDCN_ERR_INVALID, "dim must be 1, 2 or 3 (got %d)", p->dim);
+    if (p->dtype < TVDCN_F32 || p->dtype > TVDCN_BF16) return fail(TVDCN_ERR_INVALID, "unknown dtype %d", p->dtype);
+    const bool aux_ok = p->aux_dtype == p->dtype ||
+                        (p->aux_dtype == TVDCN_F32 && (p->dtype == TVDCN_F16 || p->dtype == TVDCN_BF16));
+    if (!aux_ok)
+        return fail(TVDCN_ERR_INVALID, "aux_dtype must equal dtype, or be f32 beside a 16-bit dtype (got %d / %d)",
+                    p->dtype, p->aux_dtype);
+    if (p->batch < 0 || p->in_channels <= 0 || p->out_channels <= 0)
+        return fail(TVDCN_ERR_INVALID, "batch / channel counts must be positive");
+    if (p->groups <= 0 || p->in_channels % p->groups != 0 || p->out_channels % p->groups != 0)
+        return fail(TVDCN_ERR_INVALID, "in_channels (%lld) and out_channels (%lld) must be divisible by groups (%d)",
+                    (long long)p->in_channels, (long long)p->out_channels, p->groups);
+    const int64_t cs = p->transposed ? p->out_channels : p->in_channels;
+    if (p->offset_groups < 0 || (p->offset_groups > 0 && cs % p->offset_groups != 0))
+        return fail(TVDCN_ERR_INVALID, "sampled channels (%lld) must be divisible by offset_groups (%d)",
+                    (long long)cs, p->offset_groups);
+    if (p->mask_groups < 0 || (p->mask_groups > 0 && cs % p->mask_groups != 0))
+        return fail(TVDCN_ERR_INVALID, "sampled channels (%lld) must be divisible by mask_groups (%d)",
+                    (long long)cs, p->mask_groups);
+    for (int a = 0; a < p->dim; ++a) {
+        if (p->kernel[a] <= 0 || p->stride[a] <= 0 || p->dilation[a] <= 0 || p->padding[a] < 0 ||
+            p->in_size[a] <= 0)
+            return fail(TVDCN_ERR_INVALID, "axis %d: kernel %d stride %d padding %d dilation %d in_size %lld", a,
+                        p->kernel[a], p->stride[a], p->padding[a], p->dilation[a], (long long)p->in_size[a]);
+        if (p->transposed && p->output_padding[a] < 0)
+            return fail(TVDCN_ERR_INVALID, "axis %d: negative output_padding", a);
+    }
+    return TVDCN_OK;
+}
+
+static int check_sizes(const tvdcn_problem *p) {
+    for (int a = 0; a < p->dim; ++a)
+        if (p->out_size[a] <= 0)
+            return fail(TVDCN_ERR_INVALID, "calculated output size too small (axis %d: %lld)", a,
+                        (long long)p->out_size[a]);
+    const int64_t lim = INT32_MAX;
+    if (prod(p->in_size, p->dim) > lim || prod(p->out_size, p->dim) > lim ||
+        p->batch * prod(p->in_size, p->dim) > (int64_t)1 << 40)
+        return fail(TVDCN_ERR_UNSUPPORTED, "spatial extent exceeds 32-bit per-image indexing");
+    if (p->batch > lim || p->in_channels > 1 << 20 || p->out_channels > 1 << 20)
+        return fail(TVDCN_ERR_UNSUPPORTED, "batch / channel count too large");
+    return TVDCN_OK;
+}
+
+GeoHost make_geo_host(const tvdcn_problem *p) {
+    GeoHost g;
+    memset(&g, 0, sizeof(g));
+    g.dim = p->dim;
+    g.B = (int)p->batch;
+    g.Cs = (int)(p->transposed ? p->out_channels : p->in_channels);
+    g.Cd = (int)(p->transposed ? p->in_channels : p->out_channels);
+    g.groups = p->groups;
+    g.og = p->offset_groups;
+    g.mg = p->mask_groups;
+    g.K = 1;
+    g.S = 1;
+    g.P = 1;
+    for (int a = 0; a < p->dim; ++a) {
+        g.img[a] = (int)(p->transposed ? p->out_size[a] : p->in_size[a]);
+        g.grid[a] = (int)(p->transposed ? p->in_size[a] : p->out_size[a]);
+        g.ker[a] = p->kernel[a];
+        g.stride[a] = p->stride[a];
+        g.pad[a] = p->padding[a];
+        g.dil[a] = p->dilation[a];
+        g.K *= g.ker[a];
+        g.S *= g.img[a];
+        g.P *= g.grid[a];
+    }
+    return g;
+}
+
+}  // namespace tvdcn_b200
+
+using namespace tvdcn_b200;
+
+#define CUDA_TRY(expr)                                   \
+    do {                                                 \
+        cudaError_t e__ = (expr);                        \
+        if (e__ != cudaSuccess) return cuda_fail(e__, #expr); \
+    } while (0)
+
+extern "C" {
+
+int tvdcn_b200_problem_finalize(tvdcn_problem *p) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    for (int a = 0; a < 3; ++a) p->out_size[a] = 1;
+    for (int a = 0; a < p->dim; ++a) {
+        const int64_t in = p->in_size[a], k = p->kernel[a], s = p->stride[a], pd = p->padding[a],
+                      d = p->dilation[a];
+        if (!p->transposed) {
+            const int64_t num = in + 2 * pd - (d * (k - 1) + 1);
+            p->out_size[a] = num < 0 ? 0 : num / s + 1;
+        } else {
+            p->out_size[a] = (in - 1) * s - 2 * pd + d * (k - 1) + 1 + p->output_padding[a];
+        }
+    }
+    for (int a = p->dim; a < 3; ++a) p->in_size[a] = 1;
+    return check_sizes(p);
+}
+
+size_t tvdcn_b200_forward_workspace_bytes(const tvdcn_problem *p) {
+    if (check_problem(p) || check_sizes(p)) return 0;
+    return plan_forward(p).total;
+}
+
+size_t tvdcn_b200_backward_workspace_bytes(const tvdcn_problem *p) {
+    if (check_problem(p) || check_sizes(p)) return 0;
+    return plan_backward(p, true, true, true, true).total;
+}
+
+const char *tvdcn_b200_engine_name(const tvdcn_problem *p, int backward) {
+    if (check_problem(p) || check_sizes(p)) return "invalid";
+    const Plan pl = backward ? plan_backward(p, true, true, true, true) : plan_forward(p);
+    return pl.tensor ? "tcgen05" : "simt";
+}
+
+static int check_ws(const Plan &pl, void *ws, size_t bytes) {
+    if (pl.total == 0) return TVDCN_OK;
+    if (ws == nullptr || bytes < pl.total)
+        return fail(TVDCN_ERR_WORKSPACE, "workspace of %zu bytes required, %zu given", pl.total, bytes);
+    if (reinterpret_cast<uintptr_t>(ws) % 256 != 0)
+        return fail(TVDCN_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    return TVDCN_OK;
+}
+
+int tvdcn_b200_deform_conv_forward(const tvdcn_problem *p, const void *input, const void *weight,
+                                   const void *offset, const void *mask, const void *bias, void *output,
+                                   void *workspace, size_t workspace_bytes, void *cuda_stream) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    rc = check_sizes(p);
+    if (rc) return rc;
+    if (input == nullptr || weight == nullptr || output == nullptr)
+        return fail(TVDCN_ERR_INVALID, "input, weight and output must not be NULL");
+    if ((p->offset_groups > 0) != (offset != nullptr))
+        return fail(TVDCN_ERR_INVALID, "offset pointer and offset_groups disagree");
+    if ((p->mask_groups > 0) != (mask != nullptr))
+        return fail(TVDCN_ERR_INVALID, "mask pointer and mask_groups disagree");
+    if (p->batch == 0) return TVDCN_OK;
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    const Plan pl = plan_forward(p);
+    if (p->engine == TVDCN_ENGINE_TENSOR && !pl.tensor)
+        return fail(TVDCN_ERR_UNSUPPORTED, "shape not covered by the tensor-core kernels: %s", pl.why_not);
+    rc = check_ws(pl, workspace, workspace_bytes);
+    if (rc) return rc;
+    char *ws = (char *)workspace;
+    const GeoHost g = make_geo_host(p);
+    const int dt = p->dtype, aux = p->aux_dtype;
+
+    if (pl.tensor) return tensor_forward(p, g, pl, input, weight, offset, mask, bias, output, ws, stream);
+
+    if (!p->transposed) {
+        CUDA_TRY(launch_sample_gemm(g, dt, aux, input, weight, offset, mask, bias, output, stream));
+        return TVDCN_OK;
+    }
+    // transposed: output (= sampled image) starts as the bias and receives the scatter
+    const int64_t n_out = (int64_t)g.B * g.Cs * g.S;
+    void *acc = pl.img_acc != NO_BUF ? (void *)(ws + pl.img_acc) : output;
+    CUDA_TRY(launch_fill_bias(dt, aux, bias, g.B, g.Cs, g.S, acc, stream));
+    CUDA_TRY(launch_gemm_scatter(g, dt, aux, input, weight, offset, mask, nullptr, acc, nullptr, nullptr, stream));
+    if (pl.img_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(dt, acc, output, n_out, stream));
+    return TVDCN_OK;
+}
+
+int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_output, const void *input,
+                                    const void *weight, const void *offset, const void *mask, void *grad_input,
+                                    void *grad_weight, void *grad_offset, void *grad_mask, void *grad_bias,
+                                    void *workspace, size_t workspace_bytes, void *cuda_stream) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    rc = check_sizes(p);
+    if (rc) return rc;
+    if (grad_output == nullptr || input == nullptr || weight == nullptr)
+        return fail(TVDCN_ERR_INVALID, "grad_output, input and weight must not be NULL");
+    if ((p->offset_groups > 0) != (offset != nullptr))
+        return fail(TVDCN_ERR_INVALID, "offset pointer and offset_groups disagree");
+    if ((p->mask_groups > 0) != (mask != nullptr))
+        return fail(TVDCN_ERR_INVALID, "mask pointer and mask_groups disagree");
+    if (grad_offset != nullptr && offset == nullptr)
+        return fail(TVDCN_ERR_INVALID, "grad_offset requested without offset");
+    if (grad_mask != nullptr && mask == nullptr) return fail(TVDCN_ERR_INVALID, "grad_mask requested without mask");
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    const GeoHost g = make_geo_host(p);
+    const int dt = p->dtype, aux = p->aux_dtype;
+    const size_t es = dtype_size(dt), as = dtype_size(aux);
+    const int64_t n_w = (int64_t)g.Cd * (g.Cs / g.groups) * g.K;
+    const int64_t n_off = (int64_t)g.B * g.og * g.K * g.dim * g.P;
+    const int64_t n_mask = (int64_t)g.B * g.mg * g.K * g.P;
+    const int64_t n_img = (int64_t)g.B * g.Cs * g.S;
+    const int64_t n_dense = (int64_t)g.B * g.Cd * g.P;
+    if (p->batch == 0) {
+        if (grad_weight) CUDA_TRY(cudaMemsetAsync(grad_weight, 0, n_w * es, stream));
+        if (grad_bias) CUDA_TRY(cudaMemsetAsync(grad_bias, 0, (size_t)p->out_channels * as, stream));
+        return TVDCN_OK;
+    }
+    const Plan pl = plan_backward(p, grad_input != nullptr, grad_weight != nullptr, grad_offset != nullptr,
+                                  grad_mask != nullptr);
+    if (p->engine == TVDCN_ENGINE_TENSOR && !pl.tensor)
+        return fail(TVDCN_ERR_UNSUPPORTED, "shape not covered by the tensor-core kernels: %s", pl.why_not);
+    rc = check_ws(pl, workspace, workspace_bytes);
+    if (rc) return rc;
+    char *ws = (char *)workspace;
+
+    if (pl.tensor)
+        return tensor_backward(p, g, pl, grad_output, input, weight, offset, mask, grad_input, grad_weight,
+                               grad_offset, grad_mask, grad_bias, ws, stream);
+
+    const size_t acs = dtype_size(acc_dtype(dt));
+    // accumulation targets: the outputs themselves when they already have the accumulation type
+    void *gw_acc = grad_weight ? (pl.gw_acc != NO_BUF ? (void *)(ws + pl.gw_acc) : grad_weight) : nullptr;
+    void *goff_acc = grad_offset ? (pl.goff_acc != NO_BUF ? (void *)(ws + pl.goff_acc) : grad_offset) : nullptr;
+    void *gmask_acc = grad_mask ? (pl.gmask_acc != NO_BUF ? (void *)(ws + pl.gmask_acc) : grad_mask) : nullptr;
+    if (gw_acc) CUDA_TRY(cudaMemsetAsync(gw_acc, 0, n_w * acs, stream));
+    if (goff_acc) CUDA_TRY(cudaMemsetAsync(goff_acc, 0, n_off * acs, stream));
+    if (gmask_acc) CUDA_TRY(cudaMemsetAsync(gmask_acc, 0, n_mask * acs, stream));
+
+    if (!p->transposed) {
+        // sampled image = input, dense = grad_output
+        void *gi_acc = grad_input ? (pl.img_acc != NO_BUF ? (void *)(ws + pl.img_acc) : grad_input) : nullptr;
+        if (gi_acc) CUDA_TRY(cudaMemsetAsync(gi_acc, 0, n_img * acs, stream));
+        if (gi_acc || goff_acc || gmask_acc)
+            CUDA_TRY(launch_gemm_scatter(g, dt, aux, grad_output, weight, offset, mask, input, gi_acc, goff_acc,
+                                         gmask_acc, stream));
+        if (gw_acc) CUDA_TRY(launch_sample_wgrad(g, dt, aux, grad_output, input, offset, mask, gw_acc, stream));
+        if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cd, g.P, grad_bias, stream));
+        if (gi_acc && pl.img_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(dt, gi_acc, grad_input, n_img, stream));
+    } else {
+        // sampled image = grad_output, dense = input
+        if (goff_acc || gmask_acc)
+            CUDA_TRY(launch_gemm_scatter(g, dt, aux, input, weight, offset, mask, grad_output, nullptr, goff_acc,
+                                         gmask_acc, stream));
+        if (grad_input)
+            CUDA_TRY(launch_sample_gemm(g, dt, aux, grad_output, weight, offset, mask, nullptr, grad_input, stream));
+        if (gw_acc) CUDA_TRY(launch_sample_wgrad(g, dt, aux, input, grad_output, offset, mask, gw_acc, stream));
+        if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cs, g.S, grad_bias, stream));
+        (void)n_dense;
+    }
+    if (gw_acc && pl.gw_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(dt, gw_acc, grad_weight, n_w, stream));
+    if (goff_acc && pl.goff_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(aux, goff_acc, grad_offset, n_off, stream));
+    if (gmask_acc && pl.gmask_acc != NO_BUF)
+        CUDA_TRY(launch_cast_from_acc(aux, gmask_acc, grad_mask, n_mask, stream));
+    return TVDCN_OK;
+}
+
+int tvdcn_b200_mask_softmax_forward(int32_t dtype, int64_t batch, int64_t mask_groups, int64_t taps,
+                                    int64_t spatial, const void *in, void *out, void *cuda_stream) {
+    if (dtype < TVDCN_F32 || dtype > TVDCN_BF16) return fail(TVDCN_ERR_INVALID, "unknown dtype %d", dtype);
+    if (batch < 0 || mask_groups <= 0 || taps <= 0 || spatial < 0 || taps > INT32_MAX)
+        return fail(TVDCN_ERR_INVALID, "mask_softmax: bad extents");
+    if (batch * spatial == 0) return TVDCN_OK;
+    if (in == nullptr || out == nullptr) return fail(TVDCN_ERR_INVALID, "mask_softmax: NULL pointer");
+    CUDA_TRY(launch_mask_softmax_fwd(dtype, batch * mask_groups, (int)taps, spatial, in, out,
+                                     (cudaStream_t)cuda_stream));
+    return TVDCN_OK;
+}
+
+int tvdcn_b200_mask_softmax_backward(int32_t dtype, int64_t batch, int64_t mask_groups, int64_t taps,
+                                     int64_t spatial, const void *grad_out, const void *out, void *grad_in,
+                                     void *cuda_stream) {
+    if (dtype < TVDCN_F32 || dtype > TVDCN_BF16) return fail(TVDCN_ERR_INVALID, "unknown dtype %d", dtype);
+    if (batch < 0 || mask_groups <= 0 || taps <= 0 || spatial < 0 || taps > INT32_MAX)
+        return fail(TVDCN_ERR_INVALID, "mask_softmax: bad extents");
+    if (batch * spatial == 0) return TVDCN_OK;
+    if (grad_out == nullptr || out == nullptr || grad_in == nullptr)
+        return fail(TVDCN_ERR_INVALID, "mask_softmax: NULL pointer");
+    CUDA_TRY(launch_mask_softmax_bwd(dtype, batch * mask_groups, (int)taps, spatial, grad_out, out, grad_in,
+                                     (cudaStream_t)cuda_stream));
+    return TVDCN_OK;
+}
+
+int tvdcn_b200_cuda_version(void) { return CUDART_VERSION; }
+
+const char *tvdcn_b200_cuda_arch_flags(void) { return "sm_100a"; }
+
+const char *tvdcn_b200_last_error(void) { return g_err; }
+
+uint64_t tvdcn_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"
