@@ -1,0 +1,560 @@
+#!/usr/bin/env python
+"""Benchmark of the deformable-convolution step (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config 1..5] [--mode fp32|bf16] [--impl ours|reference]
+
+One "step" is one forward + backward pass of the configured operator over one batch of seeded synthetic
+tensors (for config 2 the mask is produced by mask_softmax2d inside the step, forward and backward).
+Rank 0 prints ONE JSON line.  Keys beyond the usual ones:
+
+  value        images/s with every input already resident in HBM, all ranks together (weak scaling: each
+               rank owns a full per-GPU batch; the only exchange is the all-reduce of [grad_weight|grad_bias])
+  e2e          the same metric through the public operators (tvdcn_b200.ops.*, autograd) with HOST buffers:
+               pinned host -> device copies of the step's inputs and device -> host copies of its results
+               are inside the timed region
+  roofline     dominant kernel: algorithmic FLOPs (or bytes) per launch / CUDA-event time per launch, against
+               the measured peak in MEASURED_PEAKS.json (fallback figures if the file is absent)
+  cpu_baseline the reference's own CPU implementation (oracle/_ref) timed on this box's host cores on a
+               bounded sample of the same workload (rank 0, 1 GPU only)
+
+With --impl reference the whole run is the reference's CPU implementation on a bounded sample per step.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import math
+import os
+import sys
+import threading
+import time
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+
+@dataclass(frozen=True)
+class Config:
+    name: str
+    dim: int
+    transposed: bool
+    batch: int
+    cin: int
+    cout: int
+    in_size: Tuple[int, ...]
+    kernel: Tuple[int, ...]
+    stride: Tuple[int, ...]
+    padding: Tuple[int, ...]
+    dilation: Tuple[int, ...]
+    groups: int
+    offset_groups: int
+    mask_groups: int
+    offset_std: float
+    softmax_mask: bool
+    bound: str  # which roofline bounds the step
+
+    @property
+    def taps(self):
+        return math.prod(self.kernel)
+
+    @property
+    def out_size(self):
+        if not self.transposed:
+            return tuple((i + 2 * p - (d * (k - 1) + 1)) // s + 1 for i, k, s, p, d in
+                         zip(self.in_size, self.kernel, self.stride, self.padding, self.dilation))
+        return tuple((i - 1) * s - 2 * p + d * (k - 1) + 1 for i, k, s, p, d in
+                     zip(self.in_size, self.kernel, self.stride, self.padding, self.dilation))
+
+    @property
+    def grid(self):
+        return self.in_size if self.transposed else self.out_size
+
+    def flops_per_pass(self, batch):
+        """One GEMM pass: 2 * C_out * (C_in / groups) * taps * batch * grid positions."""
+        return 2.0 * self.cout * (self.cin / self.groups) * self.taps * batch * math.prod(self.grid)
+
+    def algorithmic_bytes(self, batch, esize=4):
+        """Every tensor of the operator's signature read or written once, forward + backward."""
+        x = batch * self.cin * math.prod(self.in_size)
+        y = batch * self.cout * math.prod(self.out_size)
+        off = batch * self.offset_groups * self.taps * self.dim * math.prod(self.grid)
+        m = batch * self.mask_groups * self.taps * math.prod(self.grid)
+        w = self.cout * self.cin // self.groups * self.taps
+        fwd = x + off + m + w + self.cout + y
+        bwd = y + x + off + m + w + x + w + off + m + self.cout
+        return (fwd + bwd) * esize
+
+
+CONFIGS = {
+    1: Config('deform_conv2d N4 C64->64 56x56 k3 s1 p1 og1 mask', 2, False, 4, 64, 64, (56, 56), (3, 3), (1, 1),
+              (1, 1), (1, 1), 1, 1, 1, 1.5, False, 'hbm'),
+    2: Config('deform_conv2d N128 C256->256 28x28 k3 s1 p1 og4 mg1 softmax-mask (DCNv2 block)', 2, False, 128, 256,
+              256, (28, 28), (3, 3), (1, 1), (1, 1), (1, 1), 1, 4, 1, 2.0, True, 'tensor'),
+    3: Config('deform_conv1d N64 C512->512 L4096 k5 d2 p4 g8 og8 mask', 1, False, 64, 512, 512, (4096,), (5,), (1,),
+              (4,), (2,), 8, 8, 1, 3.0, False, 'hbm'),
+    4: Config('deform_conv3d N8 C64->64 16x56x56 k3 s1 p1 og1 mask', 3, False, 8, 64, 64, (16, 56, 56), (3, 3, 3),
+              (1, 1, 1), (1, 1, 1), (1, 1, 1), 1, 1, 1, 1.0, False, 'tensor'),
+    5: Config('deform_conv_transpose2d N64 C256->128 32x32->64x64 k4 s2 p1 og2 mask', 2, True, 64, 256, 128,
+              (32, 32), (4, 4), (2, 2), (1, 1), (1, 1), 1, 2, 1, 1.5, False, 'tensor'),
+}
+
+
+def make_inputs(cfg: Config, batch: int, seed: int, pin: bool = False):
+    """Seeded float32 host tensors with the distributions the configuration names."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(batch, cfg.cin, *cfg.in_size, generator=g)
+    if not cfg.transposed:
+        wshape = (cfg.cout, cfg.cin // cfg.groups, *cfg.kernel)
+        fan_in = cfg.cin // cfg.groups * cfg.taps
+    else:
+        wshape = (cfg.cin, cfg.cout // cfg.groups, *cfg.kernel)
+        fan_in = cfg.cout // cfg.groups * cfg.taps
+    bound = 1.0 / math.sqrt(fan_in)  # kaiming_uniform_(a=sqrt(5)) of _ConvNd.reset_parameters
+    w = (torch.rand(*wshape, generator=g) * 2 - 1) * bound
+    bias = torch.randn(cfg.cout, generator=g) * 0.01
+    off = torch.randn(batch, cfg.offset_groups * cfg.taps * cfg.dim, *cfg.grid, generator=g) * cfg.offset_std
+    if cfg.softmax_mask:
+        m = torch.randn(batch, cfg.mask_groups * cfg.taps, *cfg.grid, generator=g)  # logits
+    else:
+        m = torch.rand(batch, cfg.mask_groups * cfg.taps, *cfg.grid, generator=g)
+    go = torch.randn(batch, cfg.cout, *cfg.out_size, generator=g)
+    ts = dict(x=x, w=w, bias=bias, off=off, m=m, go=go)
+    if pin:
+        ts = {k: v.pin_memory() for k, v in ts.items()}
+    return ts
+
+
+# ------------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    REASONS = {
+        0x8: 'hw_slowdown', 0x40: 'hw_thermal_slowdown', 0x20: 'sw_thermal_slowdown', 0x4: 'sw_power_cap',
+        0x80: 'hw_power_brake', 0x2: 'applications_clocks', 0x100: 'display_clock', 0x10: 'sync_boost',
+    }
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:  # NVML missing: report nulls
+            self._nv = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self._nv.nvmlDeviceGetClockInfo(self._h, self._nv.NVML_CLOCK_SM))
+                bits = self._nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for b, n in self.REASONS.items():
+                    if bits & b:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {'sm_mhz': s[len(s) // 2] if s else None, 'sm_max_mhz': self.max_mhz,
+                'reasons': sorted(self.reasons), 'samples': len(s)}
+
+
+# ------------------------------------------------------------------------------------------------------
+# reference (CPU) arm
+# ------------------------------------------------------------------------------------------------------
+def reference_step(cfg: Config, ts):
+    """Forward + backward with the reference's own CPU kernels (oracle/_ref), float32."""
+    name = f"deform_conv{'_transpose' if cfg.transposed else ''}{cfg.dim}d"
+    op = getattr(torch.ops.tvdcn_ref, name)
+    bop = getattr(torch.ops.tvdcn_ref, '_' + name + '_backward')
+    if cfg.transposed:
+        args = (cfg.stride, cfg.padding, (0,) * cfg.dim, cfg.dilation, cfg.groups)
+    else:
+        args = (cfg.stride, cfg.padding, cfg.dilation, cfg.groups)
+    mask = ts['m']
+    if cfg.softmax_mask:  # the reference's mask_softmax is a torch.softmax over the taps
+        b = mask.shape[0]
+        logits = mask
+        mask = torch.softmax(logits.view(b, cfg.mask_groups, cfg.taps, -1), 2).view_as(logits)
+    out = op(ts['x'], ts['w'], ts['off'], mask, ts['bias'], *args)
+    grads = bop(ts['go'], ts['x'], ts['w'], ts['off'], mask, ts['bias'], *args)
+    if cfg.softmax_mask:
+        y = mask.view(b, cfg.mask_groups, cfg.taps, -1)
+        gm = grads[3].view_as(y)
+        _ = y * (gm - (gm * y).sum(2, keepdim=True))
+    return out, grads
+
+
+def load_reference():
+    from oracle import build_ref
+    if build_ref.load():
+        return True
+    if os.path.isdir('/root/reference/tvdcn/csrc'):
+        build_ref.build('/root/reference')
+        return build_ref.load()
+    return False
+
+
+def time_reference(cfg: Config, sample_batch: int, steps: int, warmup: int, seed: int):
+    torch.set_num_threads(os.cpu_count() or 1)
+    ts = make_inputs(cfg, sample_batch, seed)
+    for _ in range(warmup):
+        reference_step(cfg, ts)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        reference_step(cfg, ts)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return sample_batch / dt, dt
+
+
+def cpu_baseline(cfg: Config, seed: int, budget_s: float = 15.0):
+    """Bounded sample of the workload on the host cores: about `budget_s` seconds of CPU work."""
+    if not load_reference():
+        return None
+    probe = min(2, cfg.batch)
+    ips, dt = time_reference(cfg, probe, 1, 1, seed)
+    per_image = dt / probe
+    nb = int(max(probe, min(cfg.batch, budget_s / 2 / max(per_image, 1e-9))))
+    ips, dt = time_reference(cfg, nb, 2, 0, seed)
+    return {'value': ips, 'unit': 'images/s', 'cores': os.cpu_count(), 'kind': 'reference',
+            'sample': f'{nb} of {cfg.batch} images of the same workload, fp32, 2 timed fwd+bwd passes, '
+                      f'{dt:.2f} s each; torch threads {torch.get_num_threads()}, '
+                      f'OpenMP loops on all {os.cpu_count()} cores, scatter loop serial as in the reference'}
+
+
+def run_reference_arm(args, cfg):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    if not load_reference():
+        print(json.dumps({'impl': 'reference', 'unavailable': 'oracle/_ref is not built and the reference '
+                          'checkout is not present on this machine'}))
+        return
+    seed = 1000 + args.config
+    probe = min(2, cfg.batch)
+    _, dt = time_reference(cfg, probe, 1, 1, seed)
+    total = max(args.steps + args.warmup, 1)
+    nb = int(max(1, min(cfg.batch, 120.0 / total / max(dt / probe, 1e-9))))
+    ips, dt = time_reference(cfg, nb, args.steps, args.warmup, seed)
+    flops = 3 * cfg.flops_per_pass(nb)
+    line = {
+        'impl': 'reference', 'metric': METRIC, 'value': ips, 'unit': 'images/s', 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt * 1e3, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic (seeded, CPU generator)',
+        'config': {'workload': cfg.name, 'sample_images_per_step': nb},
+        'effective_tflops': flops / dt / 1e12,
+        'cpu_baseline': {'value': ips, 'unit': 'images/s', 'cores': os.cpu_count(), 'kind': 'reference',
+                         'sample': f'{nb} of {cfg.batch} images per step, fp32, reference CPU kernels built from '
+                                   f'the reference sources (oracle/build_ref.py)'},
+        'e2e': {'value': ips, 'unit': 'images/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------------
+METRIC = 'deform_conv fwd+bwd images/s'
+
+
+def peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {'hbm_gbs': p['hbm_gbs'], 'tflops_burst': p['bf16_tflops'],
+                'tflops_sustained': p.get('bf16_tflops_sustained', p['bf16_tflops']), 'source': 'measured'}
+    return {'hbm_gbs': 6650.0, 'tflops_burst': 1590.0, 'tflops_sustained': 1400.0, 'source': 'fallback'}
+
+
+def known_traffic(kernel: str, config: int, mode: str):
+    """DRAM bytes per launch from a committed ncu capture (profiles/ncu_traffic.json), if there is one."""
+    path = os.path.join(ROOT, 'profiles', 'ncu_traffic.json')
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        table = json.load(f)
+    return table.get(f'{kernel}/cfg{config}/{mode}')
+
+
+class DeviceStep:
+    """The step on device-resident tensors, straight through the C ABI with preallocated outputs."""
+
+    def __init__(self, cfg: Config, ts, mode: str, device, bucket):
+        from tvdcn_b200 import cabi
+        self.cfg, self.cabi, self.L = cfg, cabi, cabi.lib()
+        dt = torch.bfloat16 if mode == 'bf16' else torch.float32
+        self.x = ts['x'].to(device, dt)
+        self.w = ts['w'].to(device, dt)
+        self.go = ts['go'].to(device, dt)
+        self.off = ts['off'].to(device)
+        self.m_in = ts['m'].to(device)
+        self.bias = ts['bias'].to(device)
+        self.mask = torch.empty_like(self.m_in) if cfg.softmax_mask else self.m_in
+        self.out = torch.empty_like(self.go)
+        self.gx = torch.empty_like(self.x)
+        self.goff = torch.empty_like(self.off)
+        self.gmask = torch.empty_like(self.mask)
+        self.glogits = torch.empty_like(self.mask) if cfg.softmax_mask else None
+        if dt == torch.float32:
+            self.gw, self.gb = bucket.weight_view, bucket.bias_view
+            self.gw16 = None
+        else:  # 16-bit weight gradient is written in bf16, then widened into the f32 bucket
+            self.gw16 = torch.empty_like(self.w)
+            self.gw, self.gb = self.gw16, bucket.bias_view
+        self.bucket = bucket
+        code = {torch.float32: cabi.F32, torch.bfloat16: cabi.BF16}[dt]
+        self.p = cabi.make_problem(cfg.dim, cfg.transposed, code, self.x.shape[0], cfg.cin, cfg.cout, cfg.in_size,
+                                   cfg.kernel, cfg.stride, cfg.padding, cfg.dilation, cfg.groups,
+                                   cfg.offset_groups, cfg.mask_groups, None, cabi.F32)
+        pp = ctypes.byref(self.p)
+        n = max(self.L.tvdcn_b200_forward_workspace_bytes(pp), self.L.tvdcn_b200_backward_workspace_bytes(pp), 256)
+        self.ws = torch.empty(n, dtype=torch.uint8, device=device)
+        self.engine = (self.L.tvdcn_b200_engine_name(pp, 0).decode(), self.L.tvdcn_b200_engine_name(pp, 1).decode())
+
+    def __call__(self):
+        cfg, L, cabi = self.cfg, self.L, self.cabi
+        vp = lambda t: ctypes.c_void_p(t.data_ptr())
+        st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        pp = ctypes.byref(self.p)
+        b = self.x.shape[0]
+        sp = math.prod(cfg.grid)
+        if cfg.softmax_mask:
+            cabi.check(L.tvdcn_b200_mask_softmax_forward(cabi.F32, b, cfg.mask_groups, cfg.taps, sp, vp(self.m_in),
+                                                         vp(self.mask), st))
+        cabi.check(L.tvdcn_b200_deform_conv_forward(pp, vp(self.x), vp(self.w), vp(self.off), vp(self.mask),
+                                                    vp(self.bias), vp(self.out), vp(self.ws), self.ws.numel(), st))
+        cabi.check(L.tvdcn_b200_deform_conv_backward(pp, vp(self.go), vp(self.x), vp(self.w), vp(self.off),
+                                                     vp(self.mask), vp(self.gx), vp(self.gw), vp(self.goff),
+                                                     vp(self.gmask), vp(self.gb), vp(self.ws), self.ws.numel(), st))
+        if self.gw16 is not None:
+            self.bucket.weight_view.copy_(self.gw16)
+        self.bucket.all_reduce_async()
+        if cfg.softmax_mask:
+            cabi.check(L.tvdcn_b200_mask_softmax_backward(cabi.F32, b, cfg.mask_groups, cfg.taps, sp, vp(self.gmask),
+                                                          vp(self.mask), vp(self.glogits), st))
+        self.bucket.wait()
+
+
+class HostStep:
+    """The step a user of the public API runs when the data lives in host memory."""
+
+    def __init__(self, cfg: Config, ts_pinned, mode: str, device, bucket):
+        import tvdcn_b200
+        self.ops = tvdcn_b200.ops
+        self.cfg, self.ts, self.mode, self.device, self.bucket = cfg, ts_pinned, mode, device, bucket
+        self.dt = torch.bfloat16 if mode == 'bf16' else torch.float32
+        self.w = ts_pinned['w'].to(device, self.dt).requires_grad_(True)
+        self.bias = ts_pinned['bias'].to(device).requires_grad_(True)
+        self.host_out = None
+        self.h2d = sum(ts_pinned[k].numel() * 4 for k in ('x', 'off', 'm', 'go'))
+        self.d2h = 0
+
+    def __call__(self):
+        cfg, ops, dev = self.cfg, self.ops, self.device
+        x = self.ts['x'].to(dev, non_blocking=True).to(self.dt).requires_grad_(True)
+        off = self.ts['off'].to(dev, non_blocking=True).requires_grad_(True)
+        m = self.ts['m'].to(dev, non_blocking=True).requires_grad_(True)
+        go = self.ts['go'].to(dev, non_blocking=True).to(self.dt)
+        mask = getattr(ops, f'mask_softmax{cfg.dim}d')(m, cfg.kernel) if cfg.softmax_mask else m
+        self.w.grad = None
+        self.bias.grad = None
+        if cfg.transposed:
+            out = getattr(ops, f'deform_conv_transpose{cfg.dim}d')(x, self.w, off, mask, self.bias, cfg.stride,
+                                                                   cfg.padding, 0, cfg.dilation, cfg.groups)
+        else:
+            out = getattr(ops, f'deform_conv{cfg.dim}d')(x, self.w, off, mask, self.bias, cfg.stride, cfg.padding,
+                                                         cfg.dilation, cfg.groups)
+        out.backward(go)
+        self.bucket.weight_view.copy_(self.w.grad)
+        self.bucket.bias_view.copy_(self.bias.grad)
+        self.bucket.all_reduce_async()
+        results = [out.detach(), x.grad, off.grad, m.grad]
+        if self.host_out is None:
+            self.host_out = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in results]
+            self.host_out.append(torch.empty(self.bucket.flat.shape, dtype=self.bucket.flat.dtype, pin_memory=True))
+            self.d2h = sum(h.numel() * h.element_size() for h in self.host_out)
+        for h, r in zip(self.host_out, results):
+            h.copy_(r, non_blocking=True)
+        self.bucket.wait()
+        self.host_out[-1].copy_(self.bucket.flat, non_blocking=True)
+
+
+def timed(fn, steps, warmup, barrier):
+    for _ in range(warmup):
+        fn()
+    barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    barrier()
+    return start.elapsed_time(stop) / 1e3  # seconds for all steps
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--config', type=int, default=2, choices=sorted(CONFIGS))
+    ap.add_argument('--mode', default='fp32', choices=['fp32', 'bf16'])
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--batch', type=int, default=0, help='per-GPU batch (default: the configuration\'s)')
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-e2e', action='store_true')
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    if args.warmup < 3 and args.impl == 'ours':
+        args.warmup = 3
+
+    if args.impl == 'reference':
+        run_reference_arm(args, cfg)
+        return
+
+    import torch.distributed as dist
+    from tvdcn_b200 import cabi
+    from tvdcn_b200.data_parallel import GradBucket
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    assert torch.cuda.is_available(), 'bench.py needs a CUDA device; there is no CPU fallback'
+    torch.cuda.set_device(local)
+    device = torch.device('cuda', local)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+
+    batch = args.batch or cfg.batch
+    seed = 1000 + args.config + 7919 * rank
+    ts = make_inputs(cfg, batch, seed, pin=not args.no_e2e)
+    wshape = ts['w'].shape
+    bucket = GradBucket(wshape, cfg.cout, dtype=torch.float32, device=device)
+    L = cabi.lib()
+    L.tvdcn_b200_timing_enable.argtypes = [ctypes.c_int]
+    L.tvdcn_b200_timing_report.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+    L.tvdcn_b200_timing_report.restype = ctypes.c_size_t
+
+    step = DeviceStep(cfg, ts, args.mode, device, bucket)
+    with ClockSampler(local) as clocks:
+        launches0 = L.tvdcn_b200_launch_count()
+        for _ in range(args.warmup):
+            step()
+        launches1 = L.tvdcn_b200_launch_count()
+        secs = timed(step, args.steps, 0, barrier)
+        launches2 = L.tvdcn_b200_launch_count()
+    t = torch.tensor([secs], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    secs = t.item()
+    value = batch * world * args.steps / secs
+
+    # per-kernel durations for the roofline: same step, kernels bracketed by CUDA events
+    L.tvdcn_b200_timing_enable(1)
+    ksteps = max(3, min(args.steps, 10))
+    for _ in range(ksteps):
+        step()
+    torch.cuda.synchronize()
+    L.tvdcn_b200_timing_enable(0)
+    buf = ctypes.create_string_buffer(1 << 14)
+    L.tvdcn_b200_timing_report(buf, len(buf))
+    kernels = {}
+    for line in buf.value.decode().splitlines():
+        name, n, ms = line.split()
+        kernels[name] = {'launches_per_step': int(n) / ksteps, 'ms_per_launch': float(ms) / int(n),
+                         'ms_per_step': float(ms) / ksteps}
+    pk = peaks()
+    gemm_like = {'sample_gemm', 'gemm_scatter', 'sample_wgrad', 'dcn_fwd_tc', 'dcn_wgrad_tc', 'dcn_dgrad_tc'}
+    dom = max(kernels, key=lambda k: kernels[k]['ms_per_step']) if kernels else None
+    roofline = None
+    if dom is not None:
+        ms = kernels[dom]['ms_per_launch']
+        if cfg.bound == 'tensor' and dom in gemm_like:
+            passes = 2 if (cfg.transposed and dom == 'gemm_scatter') else 1
+            ach = cfg.flops_per_pass(batch) / (ms / 1e3) / 1e12
+            peak = pk['tflops_sustained']
+            roofline = {'kernel': dom, 'bound': 'tensor', 'achieved': ach, 'peak': peak, 'unit': 'TFLOP/s',
+                        'frac': ach / peak, 'traffic': known_traffic(dom, args.config, args.mode),
+                        'peak_source': pk['source'] + ' bf16 dense, sustained',
+                        'note': 'algorithmic FLOPs of one GEMM pass (2*Cout*Cin/g*taps*N*P) / CUDA-event time'}
+        else:
+            # share of the step's algorithmic bytes: a GEMM-shaped kernel touches about a third of them
+            share = cfg.algorithmic_bytes(batch) / 3 if dom in gemm_like else cfg.algorithmic_bytes(batch)
+            ach = share / (ms / 1e3) / 1e9
+            roofline = {'kernel': dom, 'bound': 'hbm', 'achieved': ach, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
+                        'frac': ach / pk['hbm_gbs'], 'traffic': known_traffic(dom, args.config, args.mode),
+                        'peak_source': pk['source'] + ' copy bandwidth'}
+
+    # end to end through the public operators with host buffers
+    e2e = None
+    if not args.no_e2e:
+        host = HostStep(cfg, ts, args.mode, device, bucket)
+        esteps = max(3, min(args.steps, 10))
+        esecs = timed(host, esteps, 2, barrier)
+        t = torch.tensor([esecs], device=device, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e = {'value': batch * world * esteps / t.item(), 'unit': 'images/s', 'h2d_bytes_per_step': host.h2d,
+               'd2h_bytes_per_step': host.d2h, 'steps': esteps}
+
+    base = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        base = cpu_baseline(cfg, 1000 + args.config)
+
+    if rank == 0:
+        flops = 3 * cfg.flops_per_pass(batch) * world
+        step_s = secs / args.steps
+        nbytes = cfg.algorithmic_bytes(batch, 4) * world
+        line = {
+            'metric': METRIC, 'value': value, 'unit': 'images/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': args.warmup, 'ms_per_step': step_s * 1e3, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None,
+            'dtype': 'f32' if args.mode == 'fp32' else 'bf16 input/weight, f32 accumulate, f32 offset/mask',
+            'data': 'synthetic (seeded, CPU generator)',
+            'config': {'workload': cfg.name, 'config_index': args.config, 'per_gpu_batch': batch,
+                       'global_batch': batch * world, 'parallelism': f'dp{world}', 'engine_fwd_bwd': step.engine,
+                       'l2': 'inputs larger than L2 (no flush needed)' if nbytes / world > 126e6 * 2
+                             else 'working set near L2 size; not flushed'},
+            'effective_tflops': flops / step_s / 1e12,
+            'tensor_frac_of_peak': flops / step_s / 1e12 / pk['tflops_sustained'] / world,
+            'algorithmic_gbs': nbytes / step_s / 1e9,
+            'hbm_frac_of_peak': nbytes / step_s / 1e9 / pk['hbm_gbs'] / world,
+            'kernels': kernels, 'roofline': roofline, 'cpu_baseline': base, 'e2e': e2e,
+            'gpu_launches': int(launches2 - launches1), 'clocks': clocks.summary(),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

@@ -158,6 +158,13 @@ const char *tvdcn_b200_last_error(void);
 /* Number of kernels this library has launched in this process so far (monotonic). */
 uint64_t tvdcn_b200_launch_count(void);
 
+/* Per-kernel timing for benchmarks.  While enabled, every kernel launch of this library is bracketed by
+ * CUDA events on its stream.  tvdcn_b200_timing_report() waits for the recorded launches, writes one line
+ * per kernel name, "name launches total_ms\n", into buf (NUL-terminated, truncated to cap), clears the
+ * record and returns the untruncated length.  Do not enable it inside a stream capture. */
+void tvdcn_b200_timing_enable(int on);
+size_t tvdcn_b200_timing_report(char *buf, size_t cap);
+
 /* Name of the engine that the forward / backward call would use for this problem
  * ("simt" or "tcgen05"); for tests and benchmarks. */
 const char *tvdcn_b200_engine_name(const tvdcn_problem *p, int backward);

@@ -80,7 +80,7 @@ def make_problem(dim: int, transposed: bool, dtype: int, batch: int, in_channels
     p.dim, p.transposed, p.dtype = dim, int(transposed), dtype
     p.aux_dtype = dtype if aux_dtype is None else aux_dtype
     p.batch, p.in_channels, p.out_channels = batch, in_channels, out_channels
-    for a in range(dim):
+    for a in range(min(dim, 3, len(in_size))):
         p.in_size[a] = in_size[a]
         p.kernel[a], p.stride[a], p.padding[a], p.dilation[a] = kernel[a], stride[a], padding[a], dilation[a]
         p.output_padding[a] = output_padding[a] if output_padding is not None else 0

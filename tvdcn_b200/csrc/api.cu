@@ -3,6 +3,10 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
 
 #include "../../include/tvdcn_b200.h"
 #include "kernels.h"
@@ -12,6 +16,32 @@ namespace tvdcn_b200 {
 
 static std::atomic<uint64_t> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+// ---- optional per-kernel timing (CUDA events on the launching stream) -----------------------------
+struct TimedLaunch {
+    const char *name;
+    cudaEvent_t start, stop;
+};
+static std::atomic<int> g_timing{0};
+static std::mutex g_timing_mu;
+static std::vector<TimedLaunch> g_timed;
+
+LaunchScope::LaunchScope(const char *name, cudaStream_t stream) : name_(name), stream_(stream) {
+    count_launch();
+    if (g_timing.load(std::memory_order_relaxed)) {
+        if (cudaEventCreate(&start_) == cudaSuccess) cudaEventRecord(start_, stream_);
+        else start_ = nullptr;
+    }
+}
+
+LaunchScope::~LaunchScope() {
+    if (start_ == nullptr) return;
+    cudaEvent_t stop;
+    if (cudaEventCreate(&stop) != cudaSuccess) { cudaEventDestroy(start_); return; }
+    cudaEventRecord(stop, stream_);
+    std::lock_guard<std::mutex> lk(g_timing_mu);
+    g_timed.push_back({name_, start_, stop});
+}
 
 static thread_local char g_err[512] = "";
 
@@ -311,6 +341,40 @@ int tvdcn_b200_cuda_version(void) { return CUDART_VERSION; }
 const char *tvdcn_b200_cuda_arch_flags(void) { return "sm_100a"; }
 
 const char *tvdcn_b200_last_error(void) { return g_err; }
+
+void tvdcn_b200_timing_enable(int on) { g_timing.store(on ? 1 : 0, std::memory_order_relaxed); }
+
+size_t tvdcn_b200_timing_report(char *buf, size_t cap) {
+    std::vector<TimedLaunch> taken;
+    {
+        std::lock_guard<std::mutex> lk(g_timing_mu);
+        taken.swap(g_timed);
+    }
+    struct Agg { uint64_t n = 0; double ms = 0; };
+    std::map<std::string, Agg> agg;
+    for (auto &t : taken) {
+        float ms = 0.f;
+        if (cudaEventSynchronize(t.stop) == cudaSuccess && cudaEventElapsedTime(&ms, t.start, t.stop) == cudaSuccess) {
+            Agg &a = agg[t.name];
+            a.n += 1;
+            a.ms += ms;
+        }
+        cudaEventDestroy(t.start);
+        cudaEventDestroy(t.stop);
+    }
+    std::string out;
+    for (auto &kv : agg) {
+        char line[160];
+        snprintf(line, sizeof(line), "%s %llu %.6f\n", kv.first.c_str(), (unsigned long long)kv.second.n, kv.second.ms);
+        out += line;
+    }
+    if (buf != nullptr && cap > 0) {
+        const size_t n = out.size() < cap - 1 ? out.size() : cap - 1;
+        memcpy(buf, out.data(), n);
+        buf[n] = 0;
+    }
+    return out.size();
+}
 
 uint64_t tvdcn_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

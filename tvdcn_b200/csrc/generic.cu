@@ -482,10 +482,10 @@ cudaError_t launch_sample_gemm(const GeoHost &h, int dtype, int aux, const void 
             constexpr int DIM = decltype(dimc)::value;
             const Geo<DIM> g = make_geo<DIM>(h);
             dim3 grid((unsigned)((g.BP + BM - 1) / BM), (unsigned)(g.groups * ((g.cdg + BN - 1) / BN)));
+            LaunchScope scope("sample_gemm", stream);
             sample_gemm_kernel<T, TA, DIM><<<grid, NT, 0, stream>>>(g, (const T *)img, (const T *)weight,
                                                                     (const TA *)offset, (const TA *)mask,
                                                                     (const TA *)bias, (T *)out);
-            count_launch();
             return cudaGetLastError();
         });
     });
@@ -503,11 +503,11 @@ cudaError_t launch_gemm_scatter(const GeoHost &h, int dtype, int aux, const void
             const Geo<DIM> g = make_geo<DIM>(h);
             const int Ktot = g.csg * g.K;
             dim3 grid((unsigned)((g.BP + BM - 1) / BM), (unsigned)(g.groups * ((Ktot + BN - 1) / BN)));
+            LaunchScope scope("gemm_scatter", stream);
             gemm_scatter_kernel<T, TA, DIM><<<grid, NT, 0, stream>>>(g, (const T *)dense, (const T *)weight,
                                                                      (const TA *)offset, (const TA *)mask,
                                                                      (const T *)img, (A *)img_grad, (A *)goff,
                                                                      (A *)gmask);
-            count_launch();
             return cudaGetLastError();
         });
     });
@@ -535,10 +535,10 @@ cudaError_t launch_sample_wgrad(const GeoHost &h, int dtype, int aux, const void
             splits = (g.BP + per - 1) / per;
             dim3 grid((unsigned)((Ktot + BN - 1) / BN), (unsigned)(g.groups * ((g.cdg + BM - 1) / BM)),
                       (unsigned)splits);
+            LaunchScope scope("sample_wgrad", stream);
             sample_wgrad_kernel<T, TA, DIM><<<grid, NT, 0, stream>>>(g, (const T *)dense, (const T *)img,
                                                                      (const TA *)offset, (const TA *)mask, (A *)gw,
                                                                      per);
-            count_launch();
             return cudaGetLastError();
         });
     });
@@ -549,8 +549,8 @@ cudaError_t launch_channel_sum(int dtype, int out_dtype, const void *x, int B, i
     return dispatch_types(dtype, out_dtype, [&](auto *tp, auto *top) {
         using T = std::remove_pointer_t<decltype(tp)>;
         using TO = std::remove_pointer_t<decltype(top)>;
+        LaunchScope scope("channel_sum", stream);
         channel_sum_kernel<T, TO><<<C, 256, 0, stream>>>((const T *)x, B, C, S, (TO *)out);
-        count_launch();
         return cudaGetLastError();
     });
 }
@@ -558,13 +558,13 @@ cudaError_t launch_channel_sum(int dtype, int out_dtype, const void *x, int B, i
 cudaError_t launch_cast_from_acc(int dst_dtype, const void *src, void *dst, int64_t n, cudaStream_t stream) {
     if (n <= 0) return cudaSuccess;
     const int blocks = grid_1d(n, 256);
+    LaunchScope scope("cast", stream);
     if (dst_dtype == DT_F16)
         cast_kernel<float, __half><<<blocks, 256, 0, stream>>>((const float *)src, (__half *)dst, n);
     else if (dst_dtype == DT_BF16)
         cast_kernel<float, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const float *)src, (__nv_bfloat16 *)dst, n);
     else
         return cudaErrorInvalidValue;
-    count_launch();
     return cudaGetLastError();
 }
 
@@ -577,8 +577,8 @@ cudaError_t launch_fill_bias(int dtype, int aux, const void *bias, int B, int C,
         using T = std::remove_pointer_t<decltype(tp)>;
         using TA = std::remove_pointer_t<decltype(tap)>;
         using A = acc_t<T>;
+        LaunchScope scope("fill_bias", stream);
         fill_bias_kernel<A, TA><<<blocks, 256, 0, stream>>>((const TA *)bias, C, S, n, (A *)dst);
-        count_launch();
         return cudaGetLastError();
     });
 }

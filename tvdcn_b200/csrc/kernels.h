@@ -22,6 +22,20 @@ inline int acc_dtype(int dt) { return dt == DT_F64 ? DT_F64 : DT_F32; }
 
 void count_launch(int n = 1);
 
+// Put one of these on the stack around a kernel launch: it counts the launch and, while kernel timing is
+// switched on (tvdcn_b200_timing_enable), brackets it with CUDA events on the launching stream.
+struct LaunchScope {
+    LaunchScope(const char *name, cudaStream_t stream);
+    ~LaunchScope();
+    LaunchScope(const LaunchScope &) = delete;
+    LaunchScope &operator=(const LaunchScope &) = delete;
+
+   private:
+    const char *name_;
+    cudaStream_t stream_;
+    cudaEvent_t start_ = nullptr;
+};
+
 // ---- generic SIMT kernels (generic.cu) -------------------------------------------------
 // dense[b, d, p] = bias[d] + sum_{s', tap} W[d, s', tap] * mask * sample(img[b, s], pos)
 cudaError_t launch_sample_gemm(const GeoHost &g, int dtype, int aux_dtype, const void *img, const void *weight,

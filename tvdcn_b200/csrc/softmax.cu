@@ -164,6 +164,7 @@ template <typename T, int VEC>
 cudaError_t fwd_vec(int64_t outer, int K, int64_t P, const T *in, T *out, cudaStream_t stream) {
     const int64_t total = outer * (P / VEC);
     const int blocks = blocks_for(total);
+    LaunchScope scope("mask_softmax_fwd", stream);
     if (K <= 8)
         softmax_fwd_reg_kernel<T, VEC, 8><<<blocks, 256, 0, stream>>>(in, out, outer, K, P);
     else if (K <= 16)
@@ -172,7 +173,6 @@ cudaError_t fwd_vec(int64_t outer, int K, int64_t P, const T *in, T *out, cudaSt
         softmax_fwd_reg_kernel<T, VEC, 32><<<blocks, 256, 0, stream>>>(in, out, outer, K, P);
     else
         softmax_fwd_loop_kernel<T, VEC><<<blocks, 256, 0, stream>>>(in, out, outer, K, P);
-    count_launch();
     return cudaGetLastError();
 }
 
@@ -187,6 +187,7 @@ cudaError_t fwd_t(int64_t outer, int K, int64_t P, const void *in, void *out, cu
 template <typename T>
 cudaError_t bwd_t(int64_t outer, int K, int64_t P, const void *g, const void *y, void *gi, cudaStream_t stream) {
     constexpr int VEC = 16 / sizeof(T) > 4 ? 4 : 16 / sizeof(T);
+    LaunchScope scope("mask_softmax_bwd", stream);
     if (P % VEC == 0 && aligned(g, sizeof(T) * VEC) && aligned(y, sizeof(T) * VEC) &&
         aligned(gi, sizeof(T) * VEC)) {
         const int blocks = blocks_for(outer * (P / VEC));
@@ -195,7 +196,6 @@ cudaError_t bwd_t(int64_t outer, int K, int64_t P, const void *g, const void *y,
         const int blocks = blocks_for(outer * P);
         softmax_bwd_kernel<T, 1><<<blocks, 256, 0, stream>>>((const T *)g, (const T *)y, (T *)gi, outer, K, P);
     }
-    count_launch();
     return cudaGetLastError();
 }
 
