@@ -155,6 +155,11 @@ const char *tvdcn_b200_cuda_arch_flags(void);
 /* Message of the last failing call on this thread ("" if none). */
 const char *tvdcn_b200_last_error(void);
 
+/* Kernels with bounded waits (the tensor-core kernels wait on barriers) record a non-zero code in a
+ * per-device status word when a wait runs out instead of hanging.  This call synchronises the current
+ * device, returns the word (0 = no kernel reported a problem, -1 = the query itself failed) and clears it. */
+int tvdcn_b200_device_status(void);
+
 /* Number of kernels this library has launched in this process so far (monotonic). */
 uint64_t tvdcn_b200_launch_count(void);
 

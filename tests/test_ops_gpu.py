@@ -143,6 +143,8 @@ def test_mixed_precision_and_autocast():
 @pytest.mark.parametrize('dim', [1, 2, 3])
 def test_packed_modules_train_step(dim):
     torch.manual_seed(0)
+    torch.backends.cudnn.allow_tf32 = False  # the cuDNN convolutions below are the f32 yardstick
+    torch.backends.cuda.matmul.allow_tf32 = False
     size = (12,) * dim
     m = getattr(ops, f'PackedDeformConv{dim}d')(8, 8, 3, padding=1, offset_groups=2, mask_groups=2, modulated=True,
                                                 mask_activation='softmax').cuda()

@@ -1,0 +1,65 @@
+"""Tensor-core (tcgen05) kernels against the CPU oracle, through the C ABI.  Shapes here satisfy the
+64-channel granularity the tensor path needs; ENGINE_TENSOR makes the call fail instead of silently
+using the SIMT kernels, and the device status word must stay clean (no bounded wait ran out)."""
+import ctypes
+
+import pytest
+import torch
+
+import cases
+from cases import Case, make_inputs, nerr, run_oracle
+
+pytestmark = pytest.mark.gpu
+
+TC_CASES = [
+    Case('tc2d_c64', 2, False, 3, 64, 64, (10, 10), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 1, 1, True, 1.5),
+    Case('tc2d_c128_256', 2, False, 2, 128, 256, (9, 7), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 2, 1, True, 2.0),
+    Case('tc2d_groups', 2, False, 2, 128, 128, (8, 8), (3, 2), (2, 1), (1, 0), (1, 2), (), 2, 2, 2, True, 1.0),
+    Case('tc2d_plain', 2, False, 2, 64, 64, (8, 8), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 0, 0, False, 1.0),
+    Case('tc2d_nomask', 2, False, 2, 64, 128, (8, 8), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 1, 0, True, 1.0),
+    Case('tc1d', 1, False, 2, 128, 128, (300,), (5,), (1,), (4,), (2,), (), 2, 2, 1, True, 3.0),
+    Case('tc3d', 3, False, 1, 64, 64, (4, 6, 6), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), (), 1, 1, 1, True, 1.0),
+]
+
+
+def forward_tensor(case, x, w, off, mask, bias):
+    from tvdcn_b200 import cabi
+    L = cabi.lib()
+    L.tvdcn_b200_device_status.restype = ctypes.c_int
+    aux = torch.float32
+    p = cases.cabi_problem(case, x.dtype, aux, cabi.ENGINE_TENSOR)
+    assert L.tvdcn_b200_engine_name(ctypes.byref(p), 0) == b'tcgen05'
+    out = torch.full((case.batch, case.out_channels, *case.out_size), float('nan'), dtype=x.dtype, device='cuda')
+    n = L.tvdcn_b200_forward_workspace_bytes(ctypes.byref(p))
+    ws = torch.empty(max(n, 1), dtype=torch.uint8, device='cuda')
+    vp = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
+    cabi.check(L.tvdcn_b200_deform_conv_forward(ctypes.byref(p), vp(x), vp(w), vp(off), vp(mask), vp(bias), vp(out),
+                                                vp(ws), ws.numel(),
+                                                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    assert L.tvdcn_b200_device_status() == 0
+    return out
+
+
+@pytest.mark.parametrize('case', TC_CASES, ids=[c.name for c in TC_CASES])
+@pytest.mark.parametrize('dtype,tol', [(torch.float32, 1e-4), (torch.bfloat16, 2e-2), (torch.float16, 5e-3)],
+                         ids=['f32split', 'bf16', 'f16'])
+def test_forward_tensor(case, dtype, tol):
+    x, w, off, mask, bias, go = make_inputs(case, seed=41)
+    q = lambda t, d: None if t is None else t.to(d)
+    dev = (q(x, dtype), q(w, dtype), q(off, torch.float32), q(mask, torch.float32), q(bias, torch.float32))
+    ref = run_oracle(case, *(None if t is None else t.double() for t in dev), go)[0]
+    got = forward_tensor(case, *(None if t is None else t.cuda() for t in dev))
+    e = nerr(got, ref)
+    assert e <= tol, f'{case.name}: normalised max error {e:.3e}'
+
+
+def test_transposed_backward_uses_tensor_sample_gemm():
+    case = Case('tcT', 2, True, 2, 128, 64, (6, 6), (4, 4), (2, 2), (1, 1), (1, 1), (), 1, 1, 1, True, 1.5)
+    inputs = make_inputs(case, seed=42)
+    ref = run_oracle(case, *inputs)
+    got = cases.run_cabi(case, *(None if t is None else t.to('cuda', torch.float32) for t in inputs))
+    cases.assert_parity(got, ref, 1e-4, case.name)
+    from tvdcn_b200 import cabi
+    p = cases.cabi_problem(case, torch.float32)
+    assert cabi.lib().tvdcn_b200_engine_name(ctypes.byref(p), 1) == b'tcgen05'
+    assert cabi.lib().tvdcn_b200_device_status() == 0

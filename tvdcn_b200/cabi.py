@@ -49,7 +49,7 @@ def lib() -> C.CDLL:
             getattr(L, n).restype = sz
         L.tvdcn_b200_deform_conv_forward.argtypes = [pp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
         L.tvdcn_b200_deform_conv_forward.restype = C.c_int
-        L.tvdcn_b200_deform_conv_backward.argtypes = [pp] + [vp] * 12 + [sz, vp]
+        L.tvdcn_b200_deform_conv_backward.argtypes = [pp] + [vp] * 11 + [sz, vp]
         L.tvdcn_b200_deform_conv_backward.restype = C.c_int
         L.tvdcn_b200_mask_softmax_forward.argtypes = [i32, i64, i64, i64, i64, vp, vp, vp]
         L.tvdcn_b200_mask_softmax_forward.restype = C.c_int

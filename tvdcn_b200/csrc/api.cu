@@ -136,6 +136,41 @@ GeoHost make_geo_host(const tvdcn_problem *p) {
     return g;
 }
 
+// One status word per device, living in the library's own device memory.
+__device__ int g_tc_status;
+
+int *device_status_word() {
+    static int *cached[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (cached[dev] == nullptr) {
+        void *addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_tc_status) != cudaSuccess) return nullptr;
+        cached[dev] = (int *)addr;
+    }
+    return cached[dev];
+}
+
+// sample -> GEMM on the tensor cores: stage the image channels-last, pack the weights per tap, run.
+static cudaError_t run_sample_gemm_tc(const tvdcn_problem *p, const GeoHost &g, const Plan &pl, const void *img,
+                                      const void *weight, const void *offset, const void *mask, const void *bias,
+                                      void *out, char *ws, cudaStream_t stream) {
+    const int mode = tc_mode_of(p->dtype);
+    const int es = p->dtype == TVDCN_F32 ? 4 : 2;
+    int *status = device_status_word();
+    if (status == nullptr) return cudaErrorInvalidDevice;
+    void *img_cl = ws + pl.img_cl;
+    void *w_hi = ws + pl.w_pack;
+    void *w_lo = pl.w_pack_lo != NO_BUF ? (void *)(ws + pl.w_pack_lo) : nullptr;
+    cudaError_t e = launch_to_channels_last(img, img_cl, g.B, g.Cs, g.S, es, stream);
+    if (e != cudaSuccess) return e;
+    e = launch_pack_weight_ks(weight, p->dtype, mode, g.groups, g.Cd / g.groups, g.Cs / g.groups, g.K, w_hi, w_lo,
+                              stream);
+    if (e != cudaSuccess) return e;
+    return launch_sample_gemm_tc(g, mode, img_cl, w_hi, w_lo, (const float *)offset, (const float *)mask,
+                                 (const float *)bias, out, status, stream);
+}
+
 }  // namespace tvdcn_b200
 
 using namespace tvdcn_b200;
@@ -198,13 +233,13 @@ int tvdcn_b200_deform_conv_forward(const tvdcn_problem *p, const void *input, co
     if (rc) return rc;
     rc = check_sizes(p);
     if (rc) return rc;
+    if (p->batch == 0) return TVDCN_OK;  // nothing to compute; empty tensors may have NULL storage
     if (input == nullptr || weight == nullptr || output == nullptr)
         return fail(TVDCN_ERR_INVALID, "input, weight and output must not be NULL");
     if ((p->offset_groups > 0) != (offset != nullptr))
         return fail(TVDCN_ERR_INVALID, "offset pointer and offset_groups disagree");
     if ((p->mask_groups > 0) != (mask != nullptr))
         return fail(TVDCN_ERR_INVALID, "mask pointer and mask_groups disagree");
-    if (p->batch == 0) return TVDCN_OK;
     cudaStream_t stream = (cudaStream_t)cuda_stream;
     const Plan pl = plan_forward(p);
     if (p->engine == TVDCN_ENGINE_TENSOR && !pl.tensor)
@@ -215,7 +250,10 @@ int tvdcn_b200_deform_conv_forward(const tvdcn_problem *p, const void *input, co
     const GeoHost g = make_geo_host(p);
     const int dt = p->dtype, aux = p->aux_dtype;
 
-    if (pl.tensor) return tensor_forward(p, g, pl, input, weight, offset, mask, bias, output, ws, stream);
+    if (pl.tc_sg) {
+        CUDA_TRY(run_sample_gemm_tc(p, g, pl, input, weight, offset, mask, bias, output, ws, stream));
+        return TVDCN_OK;
+    }
 
     if (!p->transposed) {
         CUDA_TRY(launch_sample_gemm(g, dt, aux, input, weight, offset, mask, bias, output, stream));
@@ -238,15 +276,6 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
     if (rc) return rc;
     rc = check_sizes(p);
     if (rc) return rc;
-    if (grad_output == nullptr || input == nullptr || weight == nullptr)
-        return fail(TVDCN_ERR_INVALID, "grad_output, input and weight must not be NULL");
-    if ((p->offset_groups > 0) != (offset != nullptr))
-        return fail(TVDCN_ERR_INVALID, "offset pointer and offset_groups disagree");
-    if ((p->mask_groups > 0) != (mask != nullptr))
-        return fail(TVDCN_ERR_INVALID, "mask pointer and mask_groups disagree");
-    if (grad_offset != nullptr && offset == nullptr)
-        return fail(TVDCN_ERR_INVALID, "grad_offset requested without offset");
-    if (grad_mask != nullptr && mask == nullptr) return fail(TVDCN_ERR_INVALID, "grad_mask requested without mask");
     cudaStream_t stream = (cudaStream_t)cuda_stream;
     const GeoHost g = make_geo_host(p);
     const int dt = p->dtype, aux = p->aux_dtype;
@@ -259,8 +288,17 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
     if (p->batch == 0) {
         if (grad_weight) CUDA_TRY(cudaMemsetAsync(grad_weight, 0, n_w * es, stream));
         if (grad_bias) CUDA_TRY(cudaMemsetAsync(grad_bias, 0, (size_t)p->out_channels * as, stream));
-        return TVDCN_OK;
+        return TVDCN_OK;  // empty batch: the sums over the batch are zero, empty tensors may be NULL
     }
+    if (grad_output == nullptr || input == nullptr || weight == nullptr)
+        return fail(TVDCN_ERR_INVALID, "grad_output, input and weight must not be NULL");
+    if ((p->offset_groups > 0) != (offset != nullptr))
+        return fail(TVDCN_ERR_INVALID, "offset pointer and offset_groups disagree");
+    if ((p->mask_groups > 0) != (mask != nullptr))
+        return fail(TVDCN_ERR_INVALID, "mask pointer and mask_groups disagree");
+    if (grad_offset != nullptr && offset == nullptr)
+        return fail(TVDCN_ERR_INVALID, "grad_offset requested without offset");
+    if (grad_mask != nullptr && mask == nullptr) return fail(TVDCN_ERR_INVALID, "grad_mask requested without mask");
     const Plan pl = plan_backward(p, grad_input != nullptr, grad_weight != nullptr, grad_offset != nullptr,
                                   grad_mask != nullptr);
     if (p->engine == TVDCN_ENGINE_TENSOR && !pl.tensor)
@@ -268,10 +306,6 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
     rc = check_ws(pl, workspace, workspace_bytes);
     if (rc) return rc;
     char *ws = (char *)workspace;
-
-    if (pl.tensor)
-        return tensor_backward(p, g, pl, grad_output, input, weight, offset, mask, grad_input, grad_weight,
-                               grad_offset, grad_mask, grad_bias, ws, stream);
 
     const size_t acs = dtype_size(acc_dtype(dt));
     // accumulation targets: the outputs themselves when they already have the accumulation type
@@ -297,7 +331,9 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
         if (goff_acc || gmask_acc)
             CUDA_TRY(launch_gemm_scatter(g, dt, aux, input, weight, offset, mask, grad_output, nullptr, goff_acc,
                                          gmask_acc, stream));
-        if (grad_input)
+        if (grad_input && pl.tc_sg)
+            CUDA_TRY(run_sample_gemm_tc(p, g, pl, grad_output, weight, offset, mask, nullptr, grad_input, ws, stream));
+        else if (grad_input)
             CUDA_TRY(launch_sample_gemm(g, dt, aux, grad_output, weight, offset, mask, nullptr, grad_input, stream));
         if (gw_acc) CUDA_TRY(launch_sample_wgrad(g, dt, aux, input, grad_output, offset, mask, gw_acc, stream));
         if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cs, g.S, grad_bias, stream));
@@ -374,6 +410,16 @@ size_t tvdcn_b200_timing_report(char *buf, size_t cap) {
         buf[n] = 0;
     }
     return out.size();
+}
+
+int tvdcn_b200_device_status(void) {
+    int *word = device_status_word();
+    if (word == nullptr) return -1;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    int value = 0;
+    if (cudaMemcpy(&value, word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (value != 0) cudaMemset(word, 0, sizeof(int));
+    return value;
 }
 
 uint64_t tvdcn_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -1,4 +1,4 @@
-// Engine choice and workspace layout.
+// Engine choice per GEMM-shaped primitive and workspace layout.
 #include "plan.h"
 
 namespace tvdcn_b200 {
@@ -13,23 +13,69 @@ struct Bump {
     }
 };
 bool is16(int dt) { return dt == DT_F16 || dt == DT_BF16; }
+
+// Shape conditions shared by all tensor-core kernels: K chunks of 64 channels of one tap must not
+// straddle a convolution, offset or mask group, and rows of the channels-last image are indexed in 32 bits.
+const char *tc_common(const tvdcn_problem *p, const GeoHost &g) {
+    if (p->engine == TVDCN_ENGINE_SIMT) return "SIMT engine requested";
+    if (p->dtype == TVDCN_F64) return "f64 has no tensor-core kind";
+    if (p->aux_dtype != TVDCN_F32) return "offset / mask / bias must be f32 for the tensor-core kernels";
+    const int csg = g.Cs / g.groups, cdg = g.Cd / g.groups;
+    if (csg % 64 != 0) return "sampled channels per group must be a multiple of 64";
+    if (cdg % 64 != 0) return "dense channels per group must be a multiple of 64";
+    if (g.og > 0 && (g.Cs / g.og) % 64 != 0) return "channels per offset group must be a multiple of 64";
+    if (g.mg > 0 && (g.Cs / g.mg) % 64 != 0) return "channels per mask group must be a multiple of 64";
+    if ((long long)g.B * g.S >= (1LL << 31) || (long long)g.B * g.P >= (1LL << 31)) return "too many image rows";
+    return nullptr;
+}
 }  // namespace
+
+int tc_mode_of(int dtype) { return dtype == DT_F32 ? 2 : (dtype == DT_F16 ? 1 : 0); }
 
 Plan plan_forward(const tvdcn_problem *p) {
     Plan pl;
-    pl.why_not = "tensor-core forward not built yet";
     const GeoHost g = make_geo_host(p);
     Bump b;
-    if (p->transposed && is16(p->dtype)) pl.img_acc = b.take((size_t)g.B * g.Cs * g.S * sizeof(float));
+    const char *why = tc_common(p, g);
+    int bn = 0, st = 0;
+    if (why == nullptr && p->transposed) why = "tensor-core scatter kernel not available for the transposed forward";
+    if (why == nullptr && !fwd_tc_config(g.dim, tc_mode_of(p->dtype), g.Cd / g.groups, &bn, &st))
+        why = "no tile configuration fits";
+    if (why == nullptr) {
+        pl.tensor = pl.tc_sg = true;
+        const size_t es = p->dtype == TVDCN_F32 ? 4 : 2;
+        const size_t nw = (size_t)g.Cd * (g.Cs / g.groups) * g.K;
+        pl.img_cl = b.take((size_t)g.B * g.S * g.Cs * es);
+        pl.w_pack = b.take(nw * 2);
+        if (p->dtype == TVDCN_F32) pl.w_pack_lo = b.take(nw * 2);
+    } else {
+        pl.why_not = why;
+        if (p->transposed && is16(p->dtype)) pl.img_acc = b.take((size_t)g.B * g.Cs * g.S * sizeof(float));
+    }
     pl.total = b.off;
     return pl;
 }
 
 Plan plan_backward(const tvdcn_problem *p, bool want_input, bool want_weight, bool want_offset, bool want_mask) {
     Plan pl;
-    pl.why_not = "tensor-core backward not built yet";
     const GeoHost g = make_geo_host(p);
     Bump b;
+    const char *why = tc_common(p, g);
+    int bn = 0, st = 0;
+    // transposed backward: grad_input is a sample -> GEMM over grad_output
+    if (why == nullptr && !p->transposed) why = "tensor-core backward kernels not available for the convolution";
+    if (why == nullptr && !fwd_tc_config(g.dim, tc_mode_of(p->dtype), g.Cd / g.groups, &bn, &st))
+        why = "no tile configuration fits";
+    if (why == nullptr && want_input) {
+        pl.tensor = pl.tc_sg = true;
+        const size_t es = p->dtype == TVDCN_F32 ? 4 : 2;
+        const size_t nw = (size_t)g.Cd * (g.Cs / g.groups) * g.K;
+        pl.img_cl = b.take((size_t)g.B * g.S * g.Cs * es);
+        pl.w_pack = b.take(nw * 2);
+        if (p->dtype == TVDCN_F32) pl.w_pack_lo = b.take(nw * 2);
+    } else if (why != nullptr) {
+        pl.why_not = why;
+    }
     if (is16(p->dtype)) {
         if (!p->transposed && want_input) pl.img_acc = b.take((size_t)g.B * g.Cs * g.S * sizeof(float));
         if (want_weight) pl.gw_acc = b.take((size_t)g.Cd * (g.Cs / g.groups) * g.K * sizeof(float));
@@ -40,16 +86,6 @@ Plan plan_backward(const tvdcn_problem *p, bool want_input, bool want_weight, bo
     }
     pl.total = b.off;
     return pl;
-}
-
-int tensor_forward(const tvdcn_problem *, const GeoHost &, const Plan &, const void *, const void *, const void *,
-                   const void *, const void *, void *, char *, cudaStream_t) {
-    return fail(TVDCN_ERR_UNSUPPORTED, "tensor-core forward not built");
-}
-
-int tensor_backward(const tvdcn_problem *, const GeoHost &, const Plan &, const void *, const void *, const void *,
-                    const void *, const void *, void *, void *, void *, void *, void *, char *, cudaStream_t) {
-    return fail(TVDCN_ERR_UNSUPPORTED, "tensor-core backward not built");
 }
 
 }  // namespace tvdcn_b200

@@ -12,7 +12,10 @@ namespace tvdcn_b200 {
 constexpr size_t NO_BUF = (size_t)-1;
 
 struct Plan {
-    bool tensor = false;           // tensor-core (tcgen05) kernels chosen
+    bool tensor = false;           // at least one primitive runs on the tensor-core (tcgen05) kernels
+    bool tc_sg = false;            // sample -> GEMM on tensor cores
+    bool tc_gs = false;            // GEMM -> scatter / coordinate gradients on tensor cores
+    bool tc_sw = false;            // sampled weight gradient on tensor cores
     const char *why_not = "";      // reason the tensor-core kernels were not chosen
     size_t total = 0;              // workspace bytes
     // SIMT path: accumulation buffers for 16-bit outputs (byte offsets into the workspace)
@@ -20,14 +23,17 @@ struct Plan {
     size_t gw_acc = NO_BUF;
     size_t goff_acc = NO_BUF;
     size_t gmask_acc = NO_BUF;
-    // tensor path: staged copies (see sm100 kernels)
-    size_t img_cl = NO_BUF;        // sampled image, channels-last, 16-bit (hi part in split mode)
-    size_t img_cl_lo = NO_BUF;     // low part of the split
-    size_t w_pack = NO_BUF;        // weights packed per (group, tap) K-major
-    size_t w_pack_lo = NO_BUF;
-    size_t dense_cl = NO_BUF;
+    // tensor path: staged copies
+    size_t img_cl = NO_BUF;        // sampled image, channels-last (16-bit, or f32 in split mode)
+    size_t w_pack = NO_BUF;        // weights packed [g][tap][d'][s'], 16-bit (hi part in split mode)
+    size_t w_pack_lo = NO_BUF;     // low part of the split
+    size_t w_pack_kd = NO_BUF;     // weights packed [g][tap][s'][d']
+    size_t w_pack_kd_lo = NO_BUF;
+    size_t dense_cl = NO_BUF;      // dense tensor, channels-last 16-bit (hi)
     size_t dense_cl_lo = NO_BUF;
-    size_t status = NO_BUF;        // device status word written by kernels with bounded waits
+    size_t dense_hi = NO_BUF;      // dense tensor, original layout, 16-bit hi / lo (split mode)
+    size_t dense_lo = NO_BUF;
+    size_t img_grad_cl = NO_BUF;   // f32 channels-last accumulator of the scatter
 };
 
 inline size_t align_up(size_t v, size_t a = 256) { return (v + a - 1) / a * a; }
@@ -39,13 +45,20 @@ GeoHost make_geo_host(const tvdcn_problem *p);
 int fail(int code, const char *fmt, ...);
 int cuda_fail(cudaError_t e, const char *what);
 
-// tensor-core path (sm100 kernels); only called when the plan says so
-int tensor_forward(const tvdcn_problem *p, const GeoHost &g, const Plan &pl, const void *input, const void *weight,
-                   const void *offset, const void *mask, const void *bias, void *output, char *ws,
-                   cudaStream_t stream);
-int tensor_backward(const tvdcn_problem *p, const GeoHost &g, const Plan &pl, const void *grad_output,
-                    const void *input, const void *weight, const void *offset, const void *mask, void *grad_input,
-                    void *grad_weight, void *grad_offset, void *grad_mask, void *grad_bias, char *ws,
-                    cudaStream_t stream);
+// 0: bf16, 1: f16, 2: f32 split into bf16 hi + lo (the TC_* modes of the tensor-core kernels)
+int tc_mode_of(int dtype);
+
+// ---- tensor-core kernels (sm100_*.cu) -----------------------------------------------------------------
+bool fwd_tc_config(int dim, int mode, int cdg, int *bn, int *stages);
+cudaError_t launch_sample_gemm_tc(const GeoHost &g, int mode, const void *img_cl, const void *w_hi, const void *w_lo,
+                                  const float *offset, const float *mask, const float *bias, void *out, int *status,
+                                  cudaStream_t stream);
+cudaError_t launch_to_channels_last(const void *src, void *dst, int B, int C, int S, int elem_bytes,
+                                    cudaStream_t stream);
+cudaError_t launch_pack_weight_ks(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
+                                  void *lo, cudaStream_t stream);
+
+// Address of the per-device status word the tensor-core kernels report failed bounded waits in.
+int *device_status_word();
 
 }  // namespace tvdcn_b200

@@ -1,0 +1,553 @@
+// Tensor-core "sample -> GEMM" kernel (tcgen05 / TMEM), plus the layout staging kernels it needs.
+//
+//   dense[b, d, p] = bias[d] + sum_{tap, s'} W[d, s', tap] * mask * sample(img[b, s], pos(b, og(s), tap, p))
+//
+// It is an implicit GEMM  D[128 positions x BN dense channels] += A[128 x 64] * B[BN x 64]^T  over K chunks
+// of 64 channels of one kernel tap.  The A tile (the im2col columns of the reference,
+// tvdcn/csrc/ops/cuda/deform_conv2d_common_kernels.cu:138-192) is never written to global memory: four
+// producer warps sample a channels-last copy of the image straight into the 128-byte-swizzled shared
+// memory layout the tensor core reads.  The B tile (weights packed per tap) arrives by TMA.  One thread
+// issues tcgen05.mma with the accumulator in tensor memory; the producer warps then read it back
+// (tcgen05.ld: lane = position) and store NCHW with the bias added, so the reference's output_buf
+// transpose and bias pass (tvdcn/csrc/ops/cuda/deform_conv2d_kernel.cpp:371-380) are gone too.
+//
+// Warp roles (192 threads): warps 0-3 producers + epilogue, warp 4 MMA issue + TMEM owner, warp 5 TMA.
+#include <algorithm>
+#include <type_traits>
+
+#include "sm100_common.cuh"
+
+namespace tvdcn_b200 {
+
+template <int DIM>
+struct FwdParams {
+    Geo<DIM> g;
+    const void *img_cl;     // [B, S, Cs] 16-bit (TC_BF16 / TC_F16) or f32 (TC_SPLIT)
+    const float *offset;    // may be null
+    const float *mask;      // may be null
+    const float *bias;      // may be null
+    void *out;              // [B, Cd, P], data type of the problem
+    int *status;            // device status word (0 = ok)
+    int bn;                 // dense channels per tile: 64, 128 or 256
+    int stages;
+    int chunks_per_tap;     // csg / 64
+};
+
+namespace {
+
+constexpr int FWD_THREADS = 192;
+constexpr int PRODUCERS = 128;
+
+template <int DIM, int MODE>
+__global__ void __launch_bounds__(FWD_THREADS, 2)
+dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tmap_hi,
+                  const __grid_constant__ CUtensorMap tmap_lo) {
+    constexpr int NC = 1 << DIM;
+    constexpr bool SPLIT = MODE == TC_SPLIT;
+    constexpr int PARTS = SPLIT ? 2 : 1;
+    using T16 = typename std::conditional<MODE == TC_F16, __half, __nv_bfloat16>::type;
+    const Geo<DIM> &g = P.g;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int S = P.stages;
+    const int BN = P.bn;
+    const uint32_t a_stage_bytes = A_TILE_BYTES * PARTS;
+    const uint32_t b_part_bytes = (uint32_t)BN * 128u;
+    const uint32_t b_stage_bytes = b_part_bytes * PARTS;
+    uint8_t *sA = smem;
+    uint8_t *sB = sA + (size_t)S * a_stage_bytes;
+    int *plan_rows = reinterpret_cast<int *>(sB + (size_t)S * b_stage_bytes);  // [2][NC][128]
+    float *plan_wts = reinterpret_cast<float *>(plan_rows + 2 * NC * TILE_POS);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(plan_wts + 2 * NC * TILE_POS);
+    uint64_t *full_a = bars;
+    uint64_t *full_b = bars + S;
+    uint64_t *empty = bars + 2 * S;
+    uint64_t *accum = bars + 3 * S;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = g.cdg / BN;
+    const int grp = blockIdx.y / tiles_n;
+    const int n0 = (blockIdx.y % tiles_n) * BN;
+    const long long m0 = (long long)blockIdx.x * TILE_POS;
+    const int n_chunks = g.K * P.chunks_per_tap;
+    const uint32_t ncols = BN < 32 ? 32 : BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            ptx::mbar_init(&full_a[s], 4);
+            ptx::mbar_init(&full_b[s], 1);
+            ptx::mbar_init(&empty[s], 1);
+        }
+        ptx::mbar_init(accum, 1);
+        ptx::fence_mbar_init();
+    }
+    if (warp == 5 && lane == 0) {
+        ptx::prefetch_tmap(&tmap_hi);
+        if (SPLIT) ptx::prefetch_tmap(&tmap_lo);
+    }
+    if (warp == 4) {
+        ptx::tmem_alloc(tmem_slot, ncols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 4) {
+        // ------------------------------------------------------------------ producers
+        const int t = threadIdx.x;
+        const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + t);
+        int cur_tap = -1, cur_og = -1, cur_mg = -1, pb = 1;
+        bool ok = true;
+        // A failed wait never leaves the loop early: every producer keeps taking part in the named barrier
+        // below, it only stops touching shared memory and stops signalling.
+        for (int j = 0; j < n_chunks; ++j) {
+            const int s = j % S, r = j / S;
+            const int tap = j / P.chunks_per_tap, cc = j % P.chunks_per_tap;
+            const int chan0 = grp * g.csg + cc * CHUNK_C;
+            const int ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
+            const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
+            if (tap != cur_tap || ogi != cur_og || mgi != cur_mg) {
+                pb ^= 1;
+                PlanView<DIM> pv{plan_rows + pb * NC * TILE_POS, plan_wts + pb * NC * TILE_POS};
+                fill_plan<DIM>(g, pi, P.offset, P.mask, tap, ogi, mgi, t, pv);
+                cur_tap = tap; cur_og = ogi; cur_mg = mgi;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+            const int *rows = plan_rows + pb * NC * TILE_POS;
+            const float *wts = plan_wts + pb * NC * TILE_POS;
+            if (ok && !ptx::mbar_wait(&empty[s], (uint32_t)((r & 1) ^ 1))) {
+                atomicExch(P.status, 101);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the __syncwarp below
+            if (!ok) continue;
+            uint8_t *a_hi = sA + (size_t)s * a_stage_bytes;
+            if constexpr (!SPLIT) {
+                const T16 *img = reinterpret_cast<const T16 *>(P.img_cl);
+                const int oct = t & 7;
+#pragma unroll 2
+                for (int it = 0; it < 8; ++it) {
+                    const int pos = it * 16 + (t >> 3);
+                    float acc[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        const float w = wts[c * TILE_POS + pos];
+                        if (w != 0.f) {
+                            const int row = rows[c * TILE_POS + pos];
+                            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(
+                                img + (int64_t)row * g.Cs + chan0 + oct * 8));
+                            float f[8];
+                            unpack8(v, f, T16());
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, f[e], acc[e]);
+                        }
+                    }
+                    uint4 o;
+                    o.x = pack2(acc[0], acc[1], T16());
+                    o.y = pack2(acc[2], acc[3], T16());
+                    o.z = pack2(acc[4], acc[5], T16());
+                    o.w = pack2(acc[6], acc[7], T16());
+                    *reinterpret_cast<uint4 *>(a_hi + sw128_offset(pos, oct)) = o;
+                }
+            } else {
+                const float *img = reinterpret_cast<const float *>(P.img_cl);
+                uint8_t *a_lo = a_hi + A_TILE_BYTES;
+                const int quad = t & 15;
+#pragma unroll 2
+                for (int it = 0; it < 16; ++it) {
+                    const int pos = it * 8 + (t >> 4);
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        const float w = wts[c * TILE_POS + pos];
+                        if (w != 0.f) {
+                            const int row = rows[c * TILE_POS + pos];
+                            const float4 v = __ldg(reinterpret_cast<const float4 *>(
+                                img + (int64_t)row * g.Cs + chan0 + quad * 4));
+                            acc[0] = fmaf(w, v.x, acc[0]);
+                            acc[1] = fmaf(w, v.y, acc[1]);
+                            acc[2] = fmaf(w, v.z, acc[2]);
+                            acc[3] = fmaf(w, v.w, acc[3]);
+                        }
+                    }
+                    float hi[4], lo[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        hi[e] = __bfloat162float(__float2bfloat16_rn(acc[e]));
+                        lo[e] = acc[e] - hi[e];
+                    }
+                    uint2 oh, ol;
+                    oh.x = pack2(hi[0], hi[1], __nv_bfloat16());
+                    oh.y = pack2(hi[2], hi[3], __nv_bfloat16());
+                    ol.x = pack2(lo[0], lo[1], __nv_bfloat16());
+                    ol.y = pack2(lo[2], lo[3], __nv_bfloat16());
+                    const uint32_t off = sw128_offset(pos, quad >> 1) + (uint32_t)(quad & 1) * 8u;
+                    *reinterpret_cast<uint2 *>(a_hi + off) = oh;
+                    *reinterpret_cast<uint2 *>(a_lo + off) = ol;
+                }
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&full_a[s]);
+        }
+
+        // ------------------------------------------------------------------ epilogue
+        if (ok && !ptx::mbar_wait(accum, 0)) {
+            atomicExch(P.status, 102);
+            ok = false;
+        }
+        ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is a whole-warp instruction
+        ptx::tc_fence_after();
+        if (ok) {
+            const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+            for (int cb = 0; cb < BN / 32; ++cb) {
+                uint32_t v[32];
+                ptx::tmem_ld_32x32(lane_base + (uint32_t)(cb * 32), v);
+                ptx::tmem_ld_wait();
+                if (pi.valid) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const int d = grp * g.cdg + n0 + cb * 32 + e;
+                        float val = __uint_as_float(v[e]);
+                        if (P.bias != nullptr) val += __ldg(P.bias + d);
+                        const int64_t o = ((int64_t)pi.b * g.Cd + d) * (int64_t)g.P + pi.p;
+                        if constexpr (SPLIT)
+                            reinterpret_cast<float *>(P.out)[o] = val;
+                        else
+                            store_acc(reinterpret_cast<T16 *>(P.out), o, val);
+                    }
+                }
+            }
+        }
+    } else if (warp == 4) {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t idesc = ptx::instr_desc_f16(MODE == TC_F16 ? 0 : 1, TILE_POS, BN, 0, 0);
+            bool ok = true;
+            for (int j = 0; j < n_chunks && ok; ++j) {
+                const int s = j % S, r = j / S;
+                if (!ptx::mbar_wait(&full_a[s], (uint32_t)(r & 1)) || !ptx::mbar_wait(&full_b[s], (uint32_t)(r & 1))) {
+                    atomicExch(P.status, 103);
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t a_addr = ptx::smem_u32(sA + (size_t)s * a_stage_bytes);
+                const uint32_t b_addr = ptx::smem_u32(sB + (size_t)s * b_stage_bytes);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    const uint64_t a_hi = ptx::smem_desc_sw128(a_addr + k4 * 32, 16, 1024);
+                    const uint64_t b_hi = ptx::smem_desc_sw128(b_addr + k4 * 32, 16, 1024);
+                    ptx::mma_f16(tmem_base, a_hi, b_hi, idesc, (j > 0 || k4 > 0) ? 1u : 0u);
+                    if constexpr (SPLIT) {
+                        const uint64_t a_lo = ptx::smem_desc_sw128(a_addr + A_TILE_BYTES + k4 * 32, 16, 1024);
+                        const uint64_t b_lo = ptx::smem_desc_sw128(b_addr + b_part_bytes + k4 * 32, 16, 1024);
+                        ptx::mma_f16(tmem_base, a_lo, b_hi, idesc, 1u);
+                        ptx::mma_f16(tmem_base, a_hi, b_lo, idesc, 1u);
+                    }
+                }
+                ptx::mma_commit(&empty[s]);
+            }
+            if (ok) ptx::mma_commit(accum);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ TMA: weight tiles
+        if (lane == 0) {
+            int issued = 0;
+            for (int j = 0; j < n_chunks; ++j) {
+                const int s = j % S, r = j / S;
+                if (!ptx::mbar_wait(&empty[s], (uint32_t)((r & 1) ^ 1))) {
+                    atomicExch(P.status, 104);
+                    break;
+                }
+                const int tap = j / P.chunks_per_tap, cc = j % P.chunks_per_tap;
+                uint8_t *b_dst = sB + (size_t)s * b_stage_bytes;
+                ptx::mbar_arrive_expect_tx(&full_b[s], b_stage_bytes);
+                ptx::tma_load_4d(b_dst, &tmap_hi, &full_b[s], cc * CHUNK_C, n0, tap, grp);
+                if (SPLIT) ptx::tma_load_4d(b_dst + b_part_bytes, &tmap_lo, &full_b[s], cc * CHUNK_C, n0, tap, grp);
+                issued = j + 1;
+            }
+            // never leave with a copy still in flight into this CTA's shared memory
+            if (issued > 0) {
+                const int j = issued - 1;
+                ptx::mbar_wait(&full_b[j % S], (uint32_t)((j / S) & 1));
+            }
+        }
+        __syncwarp();
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 4) ptx::tmem_dealloc(tmem_base, ncols);
+}
+
+// ---- staging kernels ---------------------------------------------------------------------------------
+// [B, C, S] -> [B, S, C] through a 32 x 33 shared tile; ET is an unsigned type of the element size.
+template <typename ET>
+__global__ void __launch_bounds__(256) to_channels_last_kernel(const ET *__restrict__ src, ET *__restrict__ dst, int C,
+                                                               int S) {
+    __shared__ ET tile[32][33];
+    const int b = blockIdx.z;
+    const int s0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    const ET *in = src + (int64_t)b * C * S;
+    ET *out = dst + (int64_t)b * C * S;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = c0 + ty + 8 * i, s = s0 + tx;
+        if (c < C && s < S) tile[ty + 8 * i][tx] = in[(int64_t)c * S + s];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int s = s0 + ty + 8 * i, c = c0 + tx;
+        if (c < C && s < S) out[(int64_t)s * C + c] = tile[tx][ty + 8 * i];
+    }
+}
+
+// [B, S, C] f32 -> [B, C, S] in the destination type.
+template <typename TO>
+__global__ void __launch_bounds__(256) from_channels_last_kernel(const float *__restrict__ src, TO *__restrict__ dst,
+                                                                 int C, int S) {
+    __shared__ float tile[32][33];
+    const int b = blockIdx.z;
+    const int s0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const float *in = src + (int64_t)b * C * S;
+    TO *out = dst + (int64_t)b * C * S;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int s = s0 + ty + 8 * i, c = c0 + tx;
+        if (c < C && s < S) tile[ty + 8 * i][tx] = in[(int64_t)s * C + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = c0 + ty + 8 * i, s = s0 + tx;
+        if (c < C && s < S) store_acc(out, (int64_t)c * S + s, tile[tx][ty + 8 * i]);
+    }
+}
+
+// weight [Cd, csg, K] -> hi/lo [g][tap][d'][s'] (KS = true) or [g][tap][s'][d'] (KS = false)
+template <typename TW, bool KS>
+__global__ void pack_weight_kernel(const TW *__restrict__ w, int mode, int groups, int cdg, int csg, int K,
+                                   uint16_t *__restrict__ hi, uint16_t *__restrict__ lo) {
+    const int64_t n = (int64_t)groups * K * cdg * csg;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t r = i;
+        int dl, sl;
+        if (KS) {
+            sl = (int)(r % csg); r /= csg;
+            dl = (int)(r % cdg); r /= cdg;
+        } else {
+            dl = (int)(r % cdg); r /= cdg;
+            sl = (int)(r % csg); r /= csg;
+        }
+        const int tap = (int)(r % K);
+        const int grp = (int)(r / K);
+        const float v = to_acc(w[((int64_t)(grp * cdg + dl) * csg + sl) * K + tap]);
+        if (mode == TC_F16) {
+            const __half h = __float2half_rn(v);
+            hi[i] = *reinterpret_cast<const uint16_t *>(&h);
+        } else {
+            const __nv_bfloat16 h = __float2bfloat16_rn(v);
+            hi[i] = *reinterpret_cast<const uint16_t *>(&h);
+            if (mode == TC_SPLIT) {
+                const __nv_bfloat16 l = __float2bfloat16_rn(v - __bfloat162float(h));
+                lo[i] = *reinterpret_cast<const uint16_t *>(&l);
+            }
+        }
+    }
+}
+
+template <bool KS>
+cudaError_t launch_pack_weight(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
+                               void *lo, cudaStream_t stream) {
+    const int64_t n = (int64_t)groups * K * cdg * csg;
+    const int blocks = (int)std::min<int64_t>((n + 255) / 256, 148 * 8);
+    LaunchScope scope("pack_weight", stream);
+    if (dtype == DT_F32)
+        pack_weight_kernel<float, KS><<<blocks, 256, 0, stream>>>((const float *)w, mode, groups, cdg, csg, K,
+                                                                 (uint16_t *)hi, (uint16_t *)lo);
+    else if (dtype == DT_BF16)
+        pack_weight_kernel<__nv_bfloat16, KS><<<blocks, 256, 0, stream>>>((const __nv_bfloat16 *)w, mode, groups, cdg,
+                                                                         csg, K, (uint16_t *)hi, (uint16_t *)lo);
+    else if (dtype == DT_F16)
+        pack_weight_kernel<__half, KS><<<blocks, 256, 0, stream>>>((const __half *)w, mode, groups, cdg, csg, K,
+                                                                  (uint16_t *)hi, (uint16_t *)lo);
+    else
+        return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_pack_weight_ks(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
+                                  void *lo, cudaStream_t stream) {
+    return launch_pack_weight<true>(w, dtype, mode, groups, cdg, csg, K, hi, lo, stream);
+}
+cudaError_t launch_pack_weight_kd(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
+                                  void *lo, cudaStream_t stream) {
+    return launch_pack_weight<false>(w, dtype, mode, groups, cdg, csg, K, hi, lo, stream);
+}
+
+cudaError_t launch_to_channels_last(const void *src, void *dst, int B, int C, int S, int elem_bytes,
+                                    cudaStream_t stream) {
+    dim3 grid((S + 31) / 32, (C + 31) / 32, B);
+    LaunchScope scope("to_channels_last", stream);
+    if (elem_bytes == 2)
+        to_channels_last_kernel<uint16_t><<<grid, 256, 0, stream>>>((const uint16_t *)src, (uint16_t *)dst, C, S);
+    else if (elem_bytes == 4)
+        to_channels_last_kernel<uint32_t><<<grid, 256, 0, stream>>>((const uint32_t *)src, (uint32_t *)dst, C, S);
+    else
+        return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_from_channels_last_f32(const float *src, void *dst, int dst_dtype, int B, int C, int S,
+                                          cudaStream_t stream) {
+    dim3 grid((S + 31) / 32, (C + 31) / 32, B);
+    LaunchScope scope("from_channels_last", stream);
+    if (dst_dtype == DT_F32)
+        from_channels_last_kernel<float><<<grid, 256, 0, stream>>>(src, (float *)dst, C, S);
+    else if (dst_dtype == DT_BF16)
+        from_channels_last_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(src, (__nv_bfloat16 *)dst, C, S);
+    else if (dst_dtype == DT_F16)
+        from_channels_last_kernel<__half><<<grid, 256, 0, stream>>>(src, (__half *)dst, C, S);
+    else
+        return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+bool make_tensor_map_16bit(CUtensorMap *map, const void *base, int rank, const uint64_t *dims,
+                           const uint64_t *strides_bytes, const uint32_t *box) {
+    typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (encode == nullptr) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess || fn == nullptr)
+            return false;
+        encode = (EncodeFn)fn;
+    }
+    cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+    const CUresult rc = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void *>(base),
+                               (const cuuint64_t *)dims, (const cuuint64_t *)strides_bytes, (const cuuint32_t *)box,
+                               ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS;
+}
+
+// ---- launcher -----------------------------------------------------------------------------------------
+size_t fwd_tc_smem_bytes(int dim, int mode, int bn, int stages) {
+    const int parts = mode == TC_SPLIT ? 2 : 1;
+    const size_t stage = (size_t)(A_TILE_BYTES + bn * 128) * parts;
+    const size_t plan = (size_t)2 * (1 << dim) * TILE_POS * 8;
+    return 1024 + stages * stage + plan + (3 * stages + 1) * 8 + 16;
+}
+
+// Picks the dense-channel tile and the pipeline depth; returns false when the shape is not covered.
+bool fwd_tc_config(int dim, int mode, int cdg, int *bn, int *stages) {
+    const int cap = mode == TC_SPLIT ? 128 : 256;
+    int n = 0;
+    for (int cand : {256, 128, 64})
+        if (cand <= cap && cdg % cand == 0) { n = cand; break; }
+    if (n == 0) return false;
+    // two CTAs per SM (so one tile's epilogue overlaps another's main loop) when at least 3 stages fit in
+    // half of the 227 KB; otherwise one CTA with as many stages as fit, at most 6
+    int s = 0;
+    for (int cand = 6; cand >= 2; --cand)
+        if (fwd_tc_smem_bytes(dim, mode, n, cand) <= 113 * 1024) { s = cand; break; }
+    if (s < 3) {
+        s = 0;
+        for (int cand = 6; cand >= 2; --cand)
+            if (fwd_tc_smem_bytes(dim, mode, n, cand) <= 227 * 1024) { s = cand; break; }
+    }
+    if (s == 0) return false;
+    *bn = n;
+    *stages = s;
+    return true;
+}
+
+template <int DIM, int MODE>
+cudaError_t launch_fwd_tc_t(const GeoHost &h, const FwdParams<DIM> &P, const CUtensorMap &hi, const CUtensorMap &lo,
+                            cudaStream_t stream) {
+    const size_t smem = fwd_tc_smem_bytes(DIM, MODE, P.bn, P.stages);
+    auto kern = dcn_fwd_tc_kernel<DIM, MODE>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    const long long BP = (long long)h.B * h.P;
+    dim3 grid((unsigned)((BP + TILE_POS - 1) / TILE_POS), (unsigned)(h.groups * ((h.Cd / h.groups) / P.bn)));
+    LaunchScope scope("dcn_fwd_tc", stream);
+    kern<<<grid, FWD_THREADS, smem, stream>>>(P, hi, lo);
+    return cudaGetLastError();
+}
+
+template <int DIM>
+Geo<DIM> geo_from_host(const GeoHost &h) {
+    Geo<DIM> g;
+    g.B = h.B; g.Cs = h.Cs; g.Cd = h.Cd; g.groups = h.groups; g.og = h.og; g.mg = h.mg; g.K = h.K;
+    g.S = h.S; g.P = h.P;
+    g.csg = h.Cs / h.groups;
+    g.cdg = h.Cd / h.groups;
+    g.cs_per_og = h.og > 0 ? h.Cs / h.og : h.Cs;
+    g.cs_per_mg = h.mg > 0 ? h.Cs / h.mg : h.Cs;
+    g.BP = (long long)h.B * h.P;
+    for (int a = 0; a < DIM; ++a) {
+        g.img[a] = h.img[a]; g.grid[a] = h.grid[a]; g.ker[a] = h.ker[a];
+        g.stride[a] = h.stride[a]; g.pad[a] = h.pad[a]; g.dil[a] = h.dil[a];
+    }
+    return g;
+}
+
+// img_cl: channels-last sampled image (16-bit or f32 per mode); w_hi / w_lo: weights packed [g][tap][d'][s'].
+cudaError_t launch_sample_gemm_tc(const GeoHost &h, int mode, const void *img_cl, const void *w_hi, const void *w_lo,
+                                  const float *offset, const float *mask, const float *bias, void *out, int *status,
+                                  cudaStream_t stream) {
+    const int cdg = h.Cd / h.groups, csg = h.Cs / h.groups;
+    int bn = 0, stages = 0;
+    if (!fwd_tc_config(h.dim, mode, cdg, &bn, &stages)) return cudaErrorInvalidConfiguration;
+    CUtensorMap hi, lo;
+    const uint64_t dims[4] = {(uint64_t)csg, (uint64_t)cdg, (uint64_t)h.K, (uint64_t)h.groups};
+    const uint64_t strides[3] = {(uint64_t)csg * 2, (uint64_t)csg * cdg * 2, (uint64_t)csg * cdg * h.K * 2};
+    const uint32_t box[4] = {CHUNK_C, (uint32_t)bn, 1, 1};
+    if (!make_tensor_map_16bit(&hi, w_hi, 4, dims, strides, box)) return cudaErrorInvalidValue;
+    if (mode == TC_SPLIT) {
+        if (!make_tensor_map_16bit(&lo, w_lo, 4, dims, strides, box)) return cudaErrorInvalidValue;
+    } else {
+        lo = hi;
+    }
+    auto run = [&](auto dimc) -> cudaError_t {
+        constexpr int DIM = decltype(dimc)::value;
+        FwdParams<DIM> P;
+        P.g = geo_from_host<DIM>(h);
+        P.img_cl = img_cl;
+        P.offset = offset;
+        P.mask = mask;
+        P.bias = bias;
+        P.out = out;
+        P.status = status;
+        P.bn = bn;
+        P.stages = stages;
+        P.chunks_per_tap = csg / CHUNK_C;
+        if (mode == TC_BF16) return launch_fwd_tc_t<DIM, TC_BF16>(h, P, hi, lo, stream);
+        if (mode == TC_F16) return launch_fwd_tc_t<DIM, TC_F16>(h, P, hi, lo, stream);
+        return launch_fwd_tc_t<DIM, TC_SPLIT>(h, P, hi, lo, stream);
+    };
+    if (h.dim == 1) return run(std::integral_constant<int, 1>());
+    if (h.dim == 2) return run(std::integral_constant<int, 2>());
+    if (h.dim == 3) return run(std::integral_constant<int, 3>());
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace tvdcn_b200

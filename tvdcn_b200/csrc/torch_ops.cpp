@@ -401,7 +401,11 @@ class ConvBackwardFunction : public torch::autograd::Function<ConvBackwardFuncti
         at::AutoDispatchBelowADInplaceOrView guard;
         auto grads = Ops<D, TR>::call_backward(grad, input, weight, offset, mask, bias, stride, padding,
                                                output_padding, dilation, groups);
-        return {std::get<0>(grads), std::get<1>(grads), std::get<2>(grads), std::get<3>(grads), std::get<4>(grads)};
+        // autograd cannot wrap undefined outputs: absent gradients travel as empty tensors and are
+        // turned back into undefined ones by the caller
+        auto placeholder = [&](const Tensor &t) { return t.defined() ? t : at::empty({0}, input.options()); };
+        return {std::get<0>(grads), std::get<1>(grads), placeholder(std::get<2>(grads)),
+                placeholder(std::get<3>(grads)), placeholder(std::get<4>(grads))};
     }
     static variable_list backward(AutogradContext *, const variable_list &) {
         TORCH_CHECK(false, "double backwards on ", op_name<D, TR>(), " not supported");
@@ -428,7 +432,8 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> conv_backward_autograd(
     const OptTensor &bias, at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups) {
     auto r = ConvBackwardFunction<D, false>::apply(grad, input, weight, offset, mask, bias, stride.vec(),
                                                    padding.vec(), std::vector<int64_t>{0}, dilation.vec(), groups);
-    return std::make_tuple(r[0], r[1], r[2], r[3], r[4]);
+    return std::make_tuple(r[0], r[1], has(offset) ? r[2] : Tensor(), has(mask) ? r[3] : Tensor(),
+                           has(bias) ? r[4] : Tensor());
 }
 template <int D>
 std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> convtr_backward_autograd(
@@ -437,7 +442,8 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> convtr_backward_autograd(
     at::IntArrayRef dilation, int64_t groups) {
     auto r = ConvBackwardFunction<D, true>::apply(grad, input, weight, offset, mask, bias, stride.vec(),
                                                   padding.vec(), output_padding.vec(), dilation.vec(), groups);
-    return std::make_tuple(r[0], r[1], r[2], r[3], r[4]);
+    return std::make_tuple(r[0], r[1], has(offset) ? r[2] : Tensor(), has(mask) ? r[3] : Tensor(),
+                           has(bias) ? r[4] : Tensor());
 }
 
 // ---- CUDA key -----------------------------------------------------------------------------
