@@ -13,11 +13,11 @@ pytestmark = pytest.mark.gpu
 
 TC_CASES = [
     Case('tc2d_c64', 2, False, 3, 64, 64, (10, 10), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 1, 1, True, 1.5),
-    Case('tc2d_c128_256', 2, False, 2, 128, 256, (9, 7), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 2, 1, True, 2.0),
+    Case('tc2d_c128_256', 2, False, 2, 128, 256, (8, 7), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 2, 1, True, 2.0),
     Case('tc2d_groups', 2, False, 2, 128, 128, (8, 8), (3, 2), (2, 1), (1, 0), (1, 2), (), 2, 2, 2, True, 1.0),
     Case('tc2d_plain', 2, False, 2, 64, 64, (8, 8), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 0, 0, False, 1.0),
     Case('tc2d_nomask', 2, False, 2, 64, 128, (8, 8), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 1, 0, True, 1.0),
-    Case('tc1d', 1, False, 2, 128, 128, (300,), (5,), (1,), (4,), (2,), (), 2, 2, 1, True, 3.0),
+    Case('tc1d', 1, False, 2, 128, 128, (304,), (5,), (1,), (4,), (2,), (), 2, 2, 1, True, 3.0),
     Case('tc3d', 3, False, 1, 64, 64, (4, 6, 6), (3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), (), 1, 1, 1, True, 1.0),
 ]
 
@@ -53,13 +53,59 @@ def test_forward_tensor(case, dtype, tol):
     assert e <= tol, f'{case.name}: normalised max error {e:.3e}'
 
 
-def test_transposed_backward_uses_tensor_sample_gemm():
-    case = Case('tcT', 2, True, 2, 128, 64, (6, 6), (4, 4), (2, 2), (1, 1), (1, 1), (), 1, 1, 1, True, 1.5)
-    inputs = make_inputs(case, seed=42)
-    ref = run_oracle(case, *inputs)
-    got = cases.run_cabi(case, *(None if t is None else t.to('cuda', torch.float32) for t in inputs))
-    cases.assert_parity(got, ref, 1e-4, case.name)
+def kernels_launched(fn):
+    """Runs fn() with per-kernel timing on and returns ({kernel name: launches}, fn's result)."""
     from tvdcn_b200 import cabi
-    p = cases.cabi_problem(case, torch.float32)
-    assert cabi.lib().tvdcn_b200_engine_name(ctypes.byref(p), 1) == b'tcgen05'
+    L = cabi.lib()
+    L.tvdcn_b200_timing_enable.argtypes = [ctypes.c_int]
+    L.tvdcn_b200_timing_report.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+    L.tvdcn_b200_timing_report.restype = ctypes.c_size_t
+    buf = ctypes.create_string_buffer(1 << 14)
+    L.tvdcn_b200_timing_report(buf, len(buf))  # drop anything recorded earlier
+    L.tvdcn_b200_timing_enable(1)
+    try:
+        out = fn()
+        torch.cuda.synchronize()
+    finally:
+        L.tvdcn_b200_timing_enable(0)
+    L.tvdcn_b200_timing_report(buf, len(buf))
+    names = {}
+    for line in buf.value.decode().splitlines():
+        n, c, _ = line.split()
+        names[n] = int(c)
+    return names, out
+
+
+@pytest.mark.parametrize('case', TC_CASES, ids=[c.name for c in TC_CASES])
+@pytest.mark.parametrize('dtype,tol', [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)], ids=['f32split', 'bf16'])
+def test_forward_backward_all_tensor(case, dtype, tol):
+    x, w, off, mask, bias, go = make_inputs(case, seed=43)
+    q = lambda t, d: None if t is None else t.to(d)
+    dev = (q(x, dtype), q(w, dtype), q(off, torch.float32), q(mask, torch.float32), q(bias, torch.float32),
+           q(go, dtype))
+    ref = run_oracle(case, *(None if t is None else t.double() for t in dev))
+    names, got = kernels_launched(lambda: cases.run_cabi(case, *(None if t is None else t.cuda() for t in dev)))
+    assert names.get('dcn_fwd_tc', 0) == 1 and names.get('dcn_dgrad_tc', 0) == 1, names
+    assert 'sample_gemm' not in names and 'gemm_scatter' not in names, names
+    import math
+    if math.prod(case.out_size) % 8 == 0:  # row pitch of grad_output must be TMA-loadable
+        assert names.get('dcn_wgrad_tc', 0) == 1 and 'sample_wgrad' not in names, names
+    cases.assert_parity(got, ref, tol, case.name)
+    from tvdcn_b200 import cabi
+    assert cabi.lib().tvdcn_b200_device_status() == 0
+
+
+@pytest.mark.parametrize('dtype,tol', [(torch.float32, 1e-4), (torch.bfloat16, 2e-2)], ids=['f32split', 'bf16'])
+def test_transposed_all_tensor(dtype, tol):
+    case = Case('tcT', 2, True, 2, 128, 64, (6, 8), (4, 4), (2, 2), (1, 1), (1, 1), (1, 0), 1, 1, 1, True, 1.5)
+    x, w, off, mask, bias, go = make_inputs(case, seed=44)
+    q = lambda t, d: None if t is None else t.to(d)
+    dev = (q(x, dtype), q(w, dtype), q(off, torch.float32), q(mask, torch.float32), q(bias, torch.float32),
+           q(go, dtype))
+    ref = run_oracle(case, *(None if t is None else t.double() for t in dev))
+    names, got = kernels_launched(lambda: cases.run_cabi(case, *(None if t is None else t.cuda() for t in dev)))
+    # forward scatter + backward coordinate gradients, grad_input as sample -> GEMM, sampled weight gradient
+    assert names.get('dcn_dgrad_tc', 0) == 2 and names.get('dcn_fwd_tc', 0) == 1 and names.get('dcn_wgrad_tc', 0) == 1, names
+    cases.assert_parity(got, ref, tol, case.name)
+    from tvdcn_b200 import cabi
     assert cabi.lib().tvdcn_b200_device_status() == 0

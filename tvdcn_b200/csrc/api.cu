@@ -151,24 +151,99 @@ int *device_status_word() {
     return cached[dev];
 }
 
+// The channels-last copy of the sampled image is shared by every tensor-core kernel of one call; the entry
+// points reset this marker, the first user stages the image.
+static thread_local const void *t_staged_image = nullptr;
+
+static cudaError_t stage_image(const tvdcn_problem *p, const GeoHost &g, const Plan &pl, const void *img, char *ws,
+                               cudaStream_t stream) {
+    if (t_staged_image == img) return cudaSuccess;
+    const int es = p->dtype == TVDCN_F32 ? 4 : 2;
+    cudaError_t e = launch_to_channels_last(img, ws + pl.img_cl, g.B, g.Cs, g.S, es, stream);
+    if (e == cudaSuccess) t_staged_image = img;
+    return e;
+}
+
 // sample -> GEMM on the tensor cores: stage the image channels-last, pack the weights per tap, run.
 static cudaError_t run_sample_gemm_tc(const tvdcn_problem *p, const GeoHost &g, const Plan &pl, const void *img,
                                       const void *weight, const void *offset, const void *mask, const void *bias,
                                       void *out, char *ws, cudaStream_t stream) {
     const int mode = tc_mode_of(p->dtype);
-    const int es = p->dtype == TVDCN_F32 ? 4 : 2;
     int *status = device_status_word();
     if (status == nullptr) return cudaErrorInvalidDevice;
-    void *img_cl = ws + pl.img_cl;
     void *w_hi = ws + pl.w_pack;
     void *w_lo = pl.w_pack_lo != NO_BUF ? (void *)(ws + pl.w_pack_lo) : nullptr;
-    cudaError_t e = launch_to_channels_last(img, img_cl, g.B, g.Cs, g.S, es, stream);
+    cudaError_t e = stage_image(p, g, pl, img, ws, stream);
     if (e != cudaSuccess) return e;
     e = launch_pack_weight_ks(weight, p->dtype, mode, g.groups, g.Cd / g.groups, g.Cs / g.groups, g.K, w_hi, w_lo,
                               stream);
     if (e != cudaSuccess) return e;
-    return launch_sample_gemm_tc(g, mode, img_cl, w_hi, w_lo, (const float *)offset, (const float *)mask,
+    return launch_sample_gemm_tc(g, mode, ws + pl.img_cl, w_hi, w_lo, (const float *)offset, (const float *)mask,
                                  (const float *)bias, out, status, stream);
+}
+
+// GEMM -> scatter / coordinate gradients on the tensor cores.  `img` (the sampled image) is needed only for
+// goff / gmask; `scatter_out` (data type of the problem, [B, Cs, *img]) receives the scattered image plus
+// `bias`; goff / gmask are f32 outputs that the caller has zeroed.
+static cudaError_t run_gemm_scatter_tc(const tvdcn_problem *p, const GeoHost &g, const Plan &pl, const void *dense,
+                                       const void *weight, const void *offset, const void *mask, const void *img,
+                                       void *scatter_out, const void *bias, void *goff, void *gmask, char *ws,
+                                       cudaStream_t stream) {
+    const int mode = tc_mode_of(p->dtype);
+    int *status = device_status_word();
+    if (status == nullptr) return cudaErrorInvalidDevice;
+    void *d_hi = ws + pl.dense_cl;
+    void *d_lo = pl.dense_cl_lo != NO_BUF ? (void *)(ws + pl.dense_cl_lo) : nullptr;
+    void *w_hi = ws + pl.w_pack_kd;
+    void *w_lo = pl.w_pack_kd_lo != NO_BUF ? (void *)(ws + pl.w_pack_kd_lo) : nullptr;
+    cudaError_t e;
+    if (p->dtype == TVDCN_F32)
+        e = launch_to_channels_last_split((const float *)dense, d_hi, d_lo, g.B, g.Cd, g.P, stream);
+    else
+        e = launch_to_channels_last(dense, d_hi, g.B, g.Cd, g.P, 2, stream);
+    if (e != cudaSuccess) return e;
+    e = launch_pack_weight_kd(weight, p->dtype, mode, g.groups, g.Cd / g.groups, g.Cs / g.groups, g.K, w_hi, w_lo,
+                              stream);
+    if (e != cudaSuccess) return e;
+    const bool want_coord = goff != nullptr || gmask != nullptr;
+    if (want_coord) {
+        e = stage_image(p, g, pl, img, ws, stream);
+        if (e != cudaSuccess) return e;
+    }
+    float *acc = nullptr;
+    if (scatter_out != nullptr) {
+        acc = (float *)(ws + pl.img_grad_cl);
+        e = cudaMemsetAsync(acc, 0, (size_t)g.B * g.S * g.Cs * sizeof(float), stream);
+        if (e != cudaSuccess) return e;
+    }
+    e = launch_gemm_scatter_tc(g, mode, d_hi, d_lo, w_hi, w_lo, want_coord ? ws + pl.img_cl : nullptr,
+                               (const float *)offset, (const float *)mask, acc, (float *)goff, (float *)gmask, status,
+                               stream);
+    if (e != cudaSuccess) return e;
+    if (scatter_out != nullptr)
+        e = launch_from_channels_last_bias(acc, (const float *)bias, scatter_out, p->dtype, g.B, g.Cs, g.S, stream);
+    return e;
+}
+
+// sampled weight gradient on the tensor cores; `gw_acc` is zero-initialised f32
+static cudaError_t run_sample_wgrad_tc(const tvdcn_problem *p, const GeoHost &g, const Plan &pl, const void *dense,
+                                       const void *img, const void *offset, const void *mask, void *gw_acc, char *ws,
+                                       cudaStream_t stream) {
+    const int mode = tc_mode_of(p->dtype);
+    int *status = device_status_word();
+    if (status == nullptr) return cudaErrorInvalidDevice;
+    cudaError_t e = stage_image(p, g, pl, img, ws, stream);
+    if (e != cudaSuccess) return e;
+    const void *d_hi = dense, *d_lo = nullptr;
+    if (p->dtype == TVDCN_F32) {
+        e = launch_split_f32((const float *)dense, ws + pl.dense_hi, ws + pl.dense_lo, (int64_t)g.B * g.Cd * g.P,
+                             stream);
+        if (e != cudaSuccess) return e;
+        d_hi = ws + pl.dense_hi;
+        d_lo = ws + pl.dense_lo;
+    }
+    return launch_sample_wgrad_tc(g, mode, d_hi, d_lo, ws + pl.img_cl, (const float *)offset, (const float *)mask,
+                                  (float *)gw_acc, status, stream);
 }
 
 }  // namespace tvdcn_b200
@@ -247,6 +322,7 @@ int tvdcn_b200_deform_conv_forward(const tvdcn_problem *p, const void *input, co
     rc = check_ws(pl, workspace, workspace_bytes);
     if (rc) return rc;
     char *ws = (char *)workspace;
+    t_staged_image = nullptr;
     const GeoHost g = make_geo_host(p);
     const int dt = p->dtype, aux = p->aux_dtype;
 
@@ -257,6 +333,11 @@ int tvdcn_b200_deform_conv_forward(const tvdcn_problem *p, const void *input, co
 
     if (!p->transposed) {
         CUDA_TRY(launch_sample_gemm(g, dt, aux, input, weight, offset, mask, bias, output, stream));
+        return TVDCN_OK;
+    }
+    if (pl.tc_gs) {
+        CUDA_TRY(run_gemm_scatter_tc(p, g, pl, input, weight, offset, mask, nullptr, output, bias, nullptr, nullptr, ws,
+                                     stream));
         return TVDCN_OK;
     }
     // transposed: output (= sampled image) starts as the bias and receives the scatter
@@ -306,6 +387,7 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
     rc = check_ws(pl, workspace, workspace_bytes);
     if (rc) return rc;
     char *ws = (char *)workspace;
+    t_staged_image = nullptr;
 
     const size_t acs = dtype_size(acc_dtype(dt));
     // accumulation targets: the outputs themselves when they already have the accumulation type
@@ -319,23 +401,38 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
     if (!p->transposed) {
         // sampled image = input, dense = grad_output
         void *gi_acc = grad_input ? (pl.img_acc != NO_BUF ? (void *)(ws + pl.img_acc) : grad_input) : nullptr;
-        if (gi_acc) CUDA_TRY(cudaMemsetAsync(gi_acc, 0, n_img * acs, stream));
-        if (gi_acc || goff_acc || gmask_acc)
-            CUDA_TRY(launch_gemm_scatter(g, dt, aux, grad_output, weight, offset, mask, input, gi_acc, goff_acc,
-                                         gmask_acc, stream));
-        if (gw_acc) CUDA_TRY(launch_sample_wgrad(g, dt, aux, grad_output, input, offset, mask, gw_acc, stream));
+        if (pl.tc_gs) {
+            CUDA_TRY(run_gemm_scatter_tc(p, g, pl, grad_output, weight, offset, mask, input, grad_input, nullptr,
+                                         goff_acc, gmask_acc, ws, stream));
+            gi_acc = nullptr;
+        } else {
+            if (gi_acc) CUDA_TRY(cudaMemsetAsync(gi_acc, 0, n_img * acs, stream));
+            if (gi_acc || goff_acc || gmask_acc)
+                CUDA_TRY(launch_gemm_scatter(g, dt, aux, grad_output, weight, offset, mask, input, gi_acc, goff_acc,
+                                             gmask_acc, stream));
+        }
+        if (gw_acc && pl.tc_sw)
+            CUDA_TRY(run_sample_wgrad_tc(p, g, pl, grad_output, input, offset, mask, gw_acc, ws, stream));
+        else if (gw_acc)
+            CUDA_TRY(launch_sample_wgrad(g, dt, aux, grad_output, input, offset, mask, gw_acc, stream));
         if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cd, g.P, grad_bias, stream));
         if (gi_acc && pl.img_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(dt, gi_acc, grad_input, n_img, stream));
     } else {
         // sampled image = grad_output, dense = input
-        if (goff_acc || gmask_acc)
+        if ((goff_acc || gmask_acc) && pl.tc_gs)
+            CUDA_TRY(run_gemm_scatter_tc(p, g, pl, input, weight, offset, mask, grad_output, nullptr, nullptr, goff_acc,
+                                         gmask_acc, ws, stream));
+        else if (goff_acc || gmask_acc)
             CUDA_TRY(launch_gemm_scatter(g, dt, aux, input, weight, offset, mask, grad_output, nullptr, goff_acc,
                                          gmask_acc, stream));
         if (grad_input && pl.tc_sg)
             CUDA_TRY(run_sample_gemm_tc(p, g, pl, grad_output, weight, offset, mask, nullptr, grad_input, ws, stream));
         else if (grad_input)
             CUDA_TRY(launch_sample_gemm(g, dt, aux, grad_output, weight, offset, mask, nullptr, grad_input, stream));
-        if (gw_acc) CUDA_TRY(launch_sample_wgrad(g, dt, aux, input, grad_output, offset, mask, gw_acc, stream));
+        if (gw_acc && pl.tc_sw)
+            CUDA_TRY(run_sample_wgrad_tc(p, g, pl, input, grad_output, offset, mask, gw_acc, ws, stream));
+        else if (gw_acc)
+            CUDA_TRY(launch_sample_wgrad(g, dt, aux, input, grad_output, offset, mask, gw_acc, stream));
         if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cs, g.S, grad_bias, stream));
         (void)n_dense;
     }

@@ -28,6 +28,19 @@ const char *tc_common(const tvdcn_problem *p, const GeoHost &g) {
     if ((long long)g.B * g.S >= (1LL << 31) || (long long)g.B * g.P >= (1LL << 31)) return "too many image rows";
     return nullptr;
 }
+
+// buffers of the GEMM -> scatter kernel
+void take_scatter_buffers(Plan &pl, Bump &b, const tvdcn_problem *p, const GeoHost &g, bool scatter) {
+    const size_t nw = (size_t)g.Cd * (g.Cs / g.groups) * g.K;
+    const size_t nd = (size_t)g.B * g.Cd * g.P;
+    pl.dense_cl = b.take(nd * 2);
+    pl.w_pack_kd = b.take(nw * 2);
+    if (p->dtype == TVDCN_F32) {
+        pl.dense_cl_lo = b.take(nd * 2);
+        pl.w_pack_kd_lo = b.take(nw * 2);
+    }
+    if (scatter) pl.img_grad_cl = b.take((size_t)g.B * g.S * g.Cs * sizeof(float));
+}
 }  // namespace
 
 int tc_mode_of(int dtype) { return dtype == DT_F32 ? 2 : (dtype == DT_F16 ? 1 : 0); }
@@ -37,18 +50,28 @@ Plan plan_forward(const tvdcn_problem *p) {
     const GeoHost g = make_geo_host(p);
     Bump b;
     const char *why = tc_common(p, g);
+    const int mode = tc_mode_of(p->dtype);
+    const size_t es = p->dtype == TVDCN_F32 ? 4 : 2;
+    const size_t nw = (size_t)g.Cd * (g.Cs / g.groups) * g.K;
     int bn = 0, st = 0;
-    if (why == nullptr && p->transposed) why = "tensor-core scatter kernel not available for the transposed forward";
-    if (why == nullptr && !fwd_tc_config(g.dim, tc_mode_of(p->dtype), g.Cd / g.groups, &bn, &st))
-        why = "no tile configuration fits";
-    if (why == nullptr) {
-        pl.tensor = pl.tc_sg = true;
-        const size_t es = p->dtype == TVDCN_F32 ? 4 : 2;
-        const size_t nw = (size_t)g.Cd * (g.Cs / g.groups) * g.K;
-        pl.img_cl = b.take((size_t)g.B * g.S * g.Cs * es);
-        pl.w_pack = b.take(nw * 2);
-        if (p->dtype == TVDCN_F32) pl.w_pack_lo = b.take(nw * 2);
-    } else {
+    if (why == nullptr && !p->transposed) {
+        if (fwd_tc_config(g.dim, mode, g.Cd / g.groups, &bn, &st)) {
+            pl.tensor = pl.tc_sg = true;
+            pl.img_cl = b.take((size_t)g.B * g.S * g.Cs * es);
+            pl.w_pack = b.take(nw * 2);
+            if (p->dtype == TVDCN_F32) pl.w_pack_lo = b.take(nw * 2);
+        } else {
+            why = "no tile configuration fits";
+        }
+    } else if (why == nullptr) {
+        if (dgrad_tc_config(mode, g.Cd / g.groups, g.Cs / g.groups, &bn, &st)) {
+            pl.tensor = pl.tc_gs = true;
+            take_scatter_buffers(pl, b, p, g, true);
+        } else {
+            why = "no tile configuration fits";
+        }
+    }
+    if (why != nullptr) {
         pl.why_not = why;
         if (p->transposed && is16(p->dtype)) pl.img_acc = b.take((size_t)g.B * g.Cs * g.S * sizeof(float));
     }
@@ -61,28 +84,45 @@ Plan plan_backward(const tvdcn_problem *p, bool want_input, bool want_weight, bo
     const GeoHost g = make_geo_host(p);
     Bump b;
     const char *why = tc_common(p, g);
-    int bn = 0, st = 0;
-    // transposed backward: grad_input is a sample -> GEMM over grad_output
-    if (why == nullptr && !p->transposed) why = "tensor-core backward kernels not available for the convolution";
-    if (why == nullptr && !fwd_tc_config(g.dim, tc_mode_of(p->dtype), g.Cd / g.groups, &bn, &st))
-        why = "no tile configuration fits";
-    if (why == nullptr && want_input) {
-        pl.tensor = pl.tc_sg = true;
-        const size_t es = p->dtype == TVDCN_F32 ? 4 : 2;
-        const size_t nw = (size_t)g.Cd * (g.Cs / g.groups) * g.K;
-        pl.img_cl = b.take((size_t)g.B * g.S * g.Cs * es);
-        pl.w_pack = b.take(nw * 2);
-        if (p->dtype == TVDCN_F32) pl.w_pack_lo = b.take(nw * 2);
-    } else if (why != nullptr) {
+    const int mode = tc_mode_of(p->dtype);
+    const size_t es = p->dtype == TVDCN_F32 ? 4 : 2;
+    const size_t nw = (size_t)g.Cd * (g.Cs / g.groups) * g.K;
+    want_offset = want_offset && g.og > 0;
+    want_mask = want_mask && g.mg > 0;
+    if (why == nullptr) {
+        int bn = 0, st = 0, ns = 0, mt = 0;
+        // transposed backward: grad_input is a sample -> GEMM over grad_output
+        if (p->transposed && want_input && fwd_tc_config(g.dim, mode, g.Cd / g.groups, &bn, &st)) {
+            pl.tc_sg = true;
+            pl.w_pack = b.take(nw * 2);
+            if (p->dtype == TVDCN_F32) pl.w_pack_lo = b.take(nw * 2);
+        }
+        if (want_weight && wgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.P, &ns, &mt, &st)) {
+            pl.tc_sw = true;
+            if (p->dtype == TVDCN_F32) {
+                pl.dense_hi = b.take((size_t)g.B * g.Cd * g.P * 2);
+                pl.dense_lo = b.take((size_t)g.B * g.Cd * g.P * 2);
+            }
+        }
+        // conv: scatter into grad_input + coordinate gradients; transposed: coordinate gradients only
+        const bool scatter = !p->transposed && want_input;
+        if ((scatter || want_offset || want_mask) && dgrad_tc_config(mode, g.Cd / g.groups, g.Cs / g.groups, &bn, &st)) {
+            pl.tc_gs = true;
+            take_scatter_buffers(pl, b, p, g, scatter);
+        }
+        pl.tensor = pl.tc_sg || pl.tc_sw || pl.tc_gs;
+        if (pl.tensor) pl.img_cl = b.take((size_t)g.B * g.S * g.Cs * es);
+        if (!pl.tensor) pl.why_not = "no tensor-core kernel covers the requested gradients for this shape";
+    } else {
         pl.why_not = why;
     }
     if (is16(p->dtype)) {
-        if (!p->transposed && want_input) pl.img_acc = b.take((size_t)g.B * g.Cs * g.S * sizeof(float));
-        if (want_weight) pl.gw_acc = b.take((size_t)g.Cd * (g.Cs / g.groups) * g.K * sizeof(float));
+        if (!p->transposed && want_input && !pl.tc_gs) pl.img_acc = b.take((size_t)g.B * g.Cs * g.S * sizeof(float));
+        if (want_weight) pl.gw_acc = b.take(nw * sizeof(float));
     }
     if (is16(p->aux_dtype)) {
-        if (want_offset && g.og > 0) pl.goff_acc = b.take((size_t)g.B * g.og * g.K * g.dim * g.P * sizeof(float));
-        if (want_mask && g.mg > 0) pl.gmask_acc = b.take((size_t)g.B * g.mg * g.K * g.P * sizeof(float));
+        if (want_offset) pl.goff_acc = b.take((size_t)g.B * g.og * g.K * g.dim * g.P * sizeof(float));
+        if (want_mask) pl.gmask_acc = b.take((size_t)g.B * g.mg * g.K * g.P * sizeof(float));
     }
     pl.total = b.off;
     return pl;

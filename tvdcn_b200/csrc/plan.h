@@ -53,6 +53,22 @@ bool fwd_tc_config(int dim, int mode, int cdg, int *bn, int *stages);
 cudaError_t launch_sample_gemm_tc(const GeoHost &g, int mode, const void *img_cl, const void *w_hi, const void *w_lo,
                                   const float *offset, const float *mask, const float *bias, void *out, int *status,
                                   cudaStream_t stream);
+bool wgrad_tc_config(int dim, int mode, int cdg, int P, int *n_sub, int *m_tiles, int *stages);
+cudaError_t launch_sample_wgrad_tc(const GeoHost &g, int mode, const void *dense_hi, const void *dense_lo,
+                                   const void *img_cl, const float *offset, const float *mask, float *gw,
+                                   int *status, cudaStream_t stream);
+bool dgrad_tc_config(int mode, int cdg, int csg, int *nb, int *b_stages);
+cudaError_t launch_gemm_scatter_tc(const GeoHost &g, int mode, const void *dense_cl_hi, const void *dense_cl_lo,
+                                   const void *w_kd_hi, const void *w_kd_lo, const void *img_cl, const float *offset,
+                                   const float *mask, float *img_grad_cl, float *goff, float *gmask, int *status,
+                                   cudaStream_t stream);
+cudaError_t launch_to_channels_last_split(const float *src, void *hi, void *lo, int B, int C, int S,
+                                          cudaStream_t stream);
+cudaError_t launch_from_channels_last_bias(const float *src, const float *bias, void *dst, int dst_dtype, int B, int C,
+                                           int S, cudaStream_t stream);
+cudaError_t launch_pack_weight_kd(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
+                                  void *lo, cudaStream_t stream);
+cudaError_t launch_split_f32(const float *src, void *hi, void *lo, int64_t n, cudaStream_t stream);
 cudaError_t launch_to_channels_last(const void *src, void *dst, int B, int C, int S, int elem_bytes,
                                     cudaStream_t stream);
 cudaError_t launch_pack_weight_ks(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,

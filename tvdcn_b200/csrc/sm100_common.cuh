@@ -7,11 +7,30 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "sm100_ptx.cuh"
 
 namespace tvdcn_b200 {
+
+template <int DIM>
+inline Geo<DIM> geo_from_host(const GeoHost &h) {
+    Geo<DIM> g;
+    g.B = h.B; g.Cs = h.Cs; g.Cd = h.Cd; g.groups = h.groups; g.og = h.og; g.mg = h.mg; g.K = h.K;
+    g.S = h.S; g.P = h.P;
+    g.csg = h.Cs / h.groups;
+    g.cdg = h.Cd / h.groups;
+    g.cs_per_og = h.og > 0 ? h.Cs / h.og : h.Cs;
+    g.cs_per_mg = h.mg > 0 ? h.Cs / h.mg : h.Cs;
+    g.BP = (long long)h.B * h.P;
+    for (int a = 0; a < DIM; ++a) {
+        g.img[a] = h.img[a]; g.grid[a] = h.grid[a]; g.ker[a] = h.ker[a];
+        g.stride[a] = h.stride[a]; g.pad[a] = h.pad[a]; g.dil[a] = h.dil[a];
+    }
+    return g;
+}
 
 // How the 16-bit tensor-core operands are derived from the user's data type.
 enum : int {
@@ -65,7 +84,7 @@ __device__ __forceinline__ PosInfo<DIM> decode_position(const Geo<DIM> &g, long 
 // Fills this thread's slot of the plan.  want_deriv == false: weights are interpolation weight * mask.
 template <int DIM>
 __device__ __forceinline__ void fill_plan(const Geo<DIM> &g, const PosInfo<DIM> &pi, const float *__restrict__ offset,
-                                          const float *__restrict__ mask, int tap, int ogi, int mgi, int slot,
+                                          const float *__restrict__ mask, int tap, int ogi, int mgi, int slot, int pstride,
                                           PlanView<DIM> pv) {
     constexpr int NC = 1 << DIM;
     int fl[DIM];
@@ -106,8 +125,8 @@ __device__ __forceinline__ void fill_plan(const Geo<DIM> &g, const PosInfo<DIM> 
             flat = flat * g.img[a] + i;
             w *= bit ? fr[a] : (1.f - fr[a]);
         }
-        pv.rows[c * TILE_POS + slot] = ok ? pi.b * g.S + flat : 0;
-        pv.wts[c * TILE_POS + slot] = ok ? w : 0.f;
+        pv.rows[c * pstride + slot] = ok ? pi.b * g.S + flat : 0;
+        pv.wts[c * pstride + slot] = ok ? w : 0.f;
     }
 }
 
@@ -135,6 +154,109 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, __nv_bfloat16) {
 __device__ __forceinline__ uint32_t pack2(float a, float b, __half) {
     const __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// Samples `npos` positions x 64 channels into a 128-byte-swizzled tile (row = position).  `rows` / `wts`
+// are one plan ([NC][TILE_POS], entry = position within the tile).  All NT threads take part; loads are
+// issued unconditionally (unused corners point at row 0 with weight 0) and in batches of up to 16 per
+// thread so that global-memory latency is overlapped instead of being paid once per corner.
+//   MODE TC_BF16 / TC_F16: img_cl is 16-bit, one tile `hi`.
+//   MODE TC_SPLIT: img_cl is f32, the blended value is split into bf16 hi + lo tiles.
+template <int NC, int MODE, int NT>
+__device__ __forceinline__ void produce_tile(uint8_t *hi, uint8_t *lo, const void *img_cl, int Cs, int chan0,
+                                             const int *rows, const float *wts, int pstride, int npos, int tid) {
+    constexpr int IB = NC >= 8 ? 2 : 4;  // positions per thread whose loads are in flight together
+    if constexpr (MODE != TC_SPLIT) {
+        using T16 = typename std::conditional<MODE == TC_F16, __half, __nv_bfloat16>::type;
+        const T16 *img = reinterpret_cast<const T16 *>(img_cl) + chan0 + (tid & 7) * 8;
+        constexpr int PPI = NT / 8;  // positions covered by one pass of all threads (8 lanes per position)
+        const int psub = tid >> 3;
+        for (int p0 = 0; p0 < npos; p0 += PPI * IB) {
+            uint4 v[IB][NC];
+            float w[IB][NC];
+#pragma unroll
+            for (int i = 0; i < IB; ++i) {
+                const int pos = p0 + i * PPI + psub;
+                if (pos < npos) {
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        w[i][c] = wts[c * pstride + pos];
+                        v[i][c] = __ldg(reinterpret_cast<const uint4 *>(img + (int64_t)rows[c * pstride + pos] * Cs));
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < IB; ++i) {
+                const int pos = p0 + i * PPI + psub;
+                if (pos < npos) {
+                    float acc[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        float f[8];
+                        unpack8(v[i][c], f, T16());
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[i][c], f[e], acc[e]);
+                    }
+                    uint4 o;
+                    o.x = pack2(acc[0], acc[1], T16());
+                    o.y = pack2(acc[2], acc[3], T16());
+                    o.z = pack2(acc[4], acc[5], T16());
+                    o.w = pack2(acc[6], acc[7], T16());
+                    *reinterpret_cast<uint4 *>(hi + sw128_offset(pos, tid & 7)) = o;
+                }
+            }
+        }
+    } else {
+        const int quad = tid & 15;
+        const float *img = reinterpret_cast<const float *>(img_cl) + chan0 + quad * 4;
+        constexpr int PPI = NT / 16;  // 16 lanes (4 channels each) per position
+        const int psub = tid >> 4;
+        for (int p0 = 0; p0 < npos; p0 += PPI * IB) {
+            float4 v[IB][NC];
+            float w[IB][NC];
+#pragma unroll
+            for (int i = 0; i < IB; ++i) {
+                const int pos = p0 + i * PPI + psub;
+                if (pos < npos) {
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        w[i][c] = wts[c * pstride + pos];
+                        v[i][c] = __ldg(reinterpret_cast<const float4 *>(img + (int64_t)rows[c * pstride + pos] * Cs));
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < IB; ++i) {
+                const int pos = p0 + i * PPI + psub;
+                if (pos < npos) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        acc[0] = fmaf(w[i][c], v[i][c].x, acc[0]);
+                        acc[1] = fmaf(w[i][c], v[i][c].y, acc[1]);
+                        acc[2] = fmaf(w[i][c], v[i][c].z, acc[2]);
+                        acc[3] = fmaf(w[i][c], v[i][c].w, acc[3]);
+                    }
+                    float h[4], l[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        h[e] = __bfloat162float(__float2bfloat16_rn(acc[e]));
+                        l[e] = acc[e] - h[e];
+                    }
+                    uint2 oh, ol;
+                    oh.x = pack2(h[0], h[1], __nv_bfloat16());
+                    oh.y = pack2(h[2], h[3], __nv_bfloat16());
+                    ol.x = pack2(l[0], l[1], __nv_bfloat16());
+                    ol.y = pack2(l[2], l[3], __nv_bfloat16());
+                    const uint32_t off = sw128_offset(pos, quad >> 1) + (uint32_t)(quad & 1) * 8u;
+                    *reinterpret_cast<uint2 *>(hi + off) = oh;
+                    *reinterpret_cast<uint2 *>(lo + off) = ol;
+                }
+            }
+        }
+    }
 }
 
 // ---- host helpers ---------------------------------------------------------------------------------

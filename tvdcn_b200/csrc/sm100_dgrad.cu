@@ -1,0 +1,594 @@
+// Tensor-core "GEMM -> scatter" kernel (tcgen05 / TMEM).
+//
+//   col[k | b, p] = sum_{d in group} W[d, k] * dense[b, d, p],   k = (tap, sampled channel)
+// consumed straight out of tensor memory, never stored:
+//   img_grad[b, s, corner]   += col * mask * corner weight                      (scatter)
+//   grad_offset[b, og, tap, axis, p] += col * mask * d sample / d axis          (needs the sampled image)
+//   grad_mask[b, mg, tap, p]         += col * sample                            (needs the sampled image)
+//
+// Replaces addmm_ + compute_grad_offset + compute_grad_mask + col2im of the reference's backward loop
+// (tvdcn/csrc/ops/cuda/deform_conv2d_kernel.cpp:519-598) and addmm_ + col2im of the transposed forward
+// (tvdcn/csrc/ops/cuda/deform_conv_transpose2d_kernel.cpp:333-362): the column buffer is never written.
+//
+// GEMM view: D[128 positions (M, TMEM lanes) x 64*nb channels of one tap (N)] over the dense channels.
+//   A = dense, channels-last [B*P, Cd] 16-bit, tile [128 pos][64 d] (K-major, TMA); all reduction chunks of
+//       the position tile stay resident in shared memory while the CTA walks the column blocks;
+//   B = weights packed [g][tap][s'][d'] (K-major, TMA ring);
+//   D = a ring of accumulators in tensor memory, so the MMA of later column blocks overlaps the epilogue.
+// Epilogue (8 warps, thread = position, two warps share a lane quadrant and split the columns): one dot
+// product <col, image corner> per corner gives both coordinate gradients; the scatter uses 16-byte vector
+// reductions into a channels-last f32 image (one red per 4 channels instead of one atomic per element).
+//
+// Warp roles (320 threads): warps 0-7 epilogue, warp 8 MMA issue + TMEM owner, warp 9 TMA.
+#include <algorithm>
+#include <type_traits>
+
+#include "plan.h"
+#include "sm100_common.cuh"
+
+namespace tvdcn_b200 {
+
+template <int DIM>
+struct DgradParams {
+    Geo<DIM> g;
+    const void *img_cl;     // sampled image, channels-last (16-bit or f32); null when no coordinate gradient is wanted
+    const float *offset;    // may be null
+    const float *mask;      // may be null
+    float *img_grad_cl;     // [B*S, Cs] f32, accumulated into; may be null
+    float *goff;            // f32, accumulated into; may be null
+    float *gmask;           // f32, accumulated into; may be null
+    int *status;
+    int nb;                 // 64-channel chunks per column block: 1 or 2
+    int rc;                 // reduction chunks: cdg / 64
+    int b_stages;
+    int chunks_per_tap;     // csg / 64
+};
+
+namespace {
+
+constexpr int DG_EPI_WARPS = 8;
+constexpr int DG_THREADS = DG_EPI_WARPS * 32 + 64;
+constexpr int DG_A_TILE = 128 * 128;   // [128 pos][64 d] 16-bit
+constexpr int DG_TMEM_COLS = 512;
+
+__device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+                 : "memory");
+}
+
+// <g[0..n), image row> for n channels starting at `src` (16-bit or f32 elements)
+template <int N, typename TI>
+struct CornerLoad;
+
+template <int N>
+struct CornerLoad<N, float> {
+    float4 v[N / 4];
+    __device__ __forceinline__ void load(const float *src) {
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) v[i] = __ldg(reinterpret_cast<const float4 *>(src) + i);
+    }
+    __device__ __forceinline__ float dot(const float *gv) const {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < N / 4; ++i) {
+            s = fmaf(gv[4 * i], v[i].x, s);
+            s = fmaf(gv[4 * i + 1], v[i].y, s);
+            s = fmaf(gv[4 * i + 2], v[i].z, s);
+            s = fmaf(gv[4 * i + 3], v[i].w, s);
+        }
+        return s;
+    }
+};
+
+template <int N, typename T16>
+struct CornerLoad {
+    uint4 v[N / 8];
+    __device__ __forceinline__ void load(const T16 *src) {
+#pragma unroll
+        for (int i = 0; i < N / 8; ++i) v[i] = __ldg(reinterpret_cast<const uint4 *>(src) + i);
+    }
+    __device__ __forceinline__ float dot(const float *gv) const {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < N / 8; ++i) {
+            float f[8];
+            unpack8(v[i], f, T16());
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s = fmaf(gv[8 * i + e], f[e], s);
+        }
+        return s;
+    }
+};
+
+template <int DIM, int MODE>
+__global__ void __launch_bounds__(DG_THREADS, 1)
+dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMap tmap_a_hi,
+                    const __grid_constant__ CUtensorMap tmap_a_lo, const __grid_constant__ CUtensorMap tmap_b_hi,
+                    const __grid_constant__ CUtensorMap tmap_b_lo) {
+    constexpr int NC = 1 << DIM;
+    constexpr bool SPLIT = MODE == TC_SPLIT;
+    constexpr int PARTS = SPLIT ? 2 : 1;
+    using TI = typename std::conditional<SPLIT, float, typename std::conditional<MODE == TC_F16, __half, __nv_bfloat16>::type>::type;
+    constexpr int ESZ = SPLIT ? 4 : 2;
+    constexpr int PS = (256 / (NC * ESZ)) < 32 ? (256 / (NC * ESZ)) : 32;  // channels per register piece
+    const Geo<DIM> &g = P.g;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int RC = P.rc, NB = P.nb, BS = P.b_stages;
+    const int ncol = NB * 64;                       // columns per accumulator
+    const int NQ = DG_TMEM_COLS / ncol;             // accumulators in the ring (8 or 4)
+    const uint32_t a_bytes = (uint32_t)(RC * PARTS * DG_A_TILE);       // [rc][part]
+    const uint32_t b_part_bytes = (uint32_t)(ncol * 128);
+    const uint32_t b_stage_bytes = b_part_bytes * PARTS;
+    uint8_t *sA = smem;
+    uint8_t *sB = sA + a_bytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sB + (size_t)BS * b_stage_bytes);
+    uint64_t *a_full = bars;
+    uint64_t *b_full = bars + 1;
+    uint64_t *b_empty = b_full + BS;
+    uint64_t *t_full = b_empty + BS;
+    uint64_t *t_empty = t_full + 8;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(t_empty + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int grp = blockIdx.y;
+    const long long m0 = (long long)blockIdx.x * TILE_POS;
+    const int blocks_per_tap = P.chunks_per_tap / NB;
+    const int n_blocks = g.K * blocks_per_tap;
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(a_full, 1);
+        for (int s = 0; s < BS; ++s) {
+            ptx::mbar_init(&b_full[s], 1);
+            ptx::mbar_init(&b_empty[s], 1);
+        }
+        for (int q = 0; q < 8; ++q) {
+            ptx::mbar_init(&t_full[q], 1);
+            ptx::mbar_init(&t_empty[q], DG_EPI_WARPS);
+        }
+        ptx::fence_mbar_init();
+    }
+    if (warp == DG_EPI_WARPS + 1 && lane == 0) {
+        ptx::prefetch_tmap(&tmap_a_hi);
+        ptx::prefetch_tmap(&tmap_b_hi);
+        if (SPLIT) {
+            ptx::prefetch_tmap(&tmap_a_lo);
+            ptx::prefetch_tmap(&tmap_b_lo);
+        }
+    }
+    if (warp == DG_EPI_WARPS) {
+        ptx::tmem_alloc(tmem_slot, DG_TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < DG_EPI_WARPS) {
+        // ------------------------------------------------------------------ epilogue
+        const int lane_q = warp & 3, half = warp >> 2;
+        const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + lane_q * 32 + lane);
+        const bool deformable = P.offset != nullptr;
+        const bool want_coord = P.goff != nullptr || P.gmask != nullptr;
+        const TI *img = reinterpret_cast<const TI *>(P.img_cl);
+        int fl[DIM];
+        float fr[DIM];
+        float mval = 1.f;
+        int cur_tap = -1, cur_og = -1, cur_mtap = -1, cur_mg = -1;
+        float go_sum[DIM], gm_sum = 0.f;
+#pragma unroll
+        for (int a = 0; a < DIM; ++a) go_sum[a] = 0.f;
+
+        auto flush_off = [&]() {
+            if (P.goff != nullptr && cur_tap >= 0 && pi.valid) {
+#pragma unroll
+                for (int a = 0; a < DIM; ++a)
+                    atomicAdd(P.goff + ((((int64_t)pi.b * g.og + cur_og) * g.K + cur_tap) * DIM + a) * (int64_t)g.P + pi.p,
+                              go_sum[a]);
+            }
+#pragma unroll
+            for (int a = 0; a < DIM; ++a) go_sum[a] = 0.f;
+        };
+        auto flush_mask = [&]() {
+            if (P.gmask != nullptr && cur_mtap >= 0 && pi.valid)
+                atomicAdd(P.gmask + (((int64_t)pi.b * g.mg + cur_mg) * g.K + cur_mtap) * (int64_t)g.P + pi.p, gm_sum);
+            gm_sum = 0.f;
+        };
+
+        bool ok = true;
+        for (int blk = 0; blk < n_blocks; ++blk) {
+            const int q = blk % NQ;
+            const int tap = blk / blocks_per_tap;
+            const int cc0 = (blk % blocks_per_tap) * NB;
+            if (ok && !ptx::mbar_wait(&t_full[q], (uint32_t)((blk / NQ) & 1))) {
+                atomicExch(P.status, 301);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            for (int ci = 0; ci < NB; ++ci) {
+                const int chan0 = grp * g.csg + (cc0 + ci) * CHUNK_C;
+                const int ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
+                const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
+                if (tap != cur_tap || ogi != cur_og) {
+                    flush_off();
+                    cur_tap = tap;
+                    cur_og = ogi;
+                    int r = tap, tc[DIM];
+#pragma unroll
+                    for (int a = DIM - 1; a >= 0; --a) {
+                        tc[a] = r % g.ker[a];
+                        r /= g.ker[a];
+                    }
+#pragma unroll
+                    for (int a = 0; a < DIM; ++a) {
+                        const int base = pi.base[a] + tc[a] * g.dil[a];
+                        if (deformable && pi.valid) {
+                            const float o = __ldg(P.offset + ((((int64_t)pi.b * g.og + ogi) * g.K + tap) * DIM + a) *
+                                                                 (int64_t)g.P + pi.p);
+                            const float pos = (float)base + o;
+                            const float f = floorf(pos);
+                            fl[a] = (int)f;
+                            fr[a] = pos - f;
+                        } else {
+                            fl[a] = base;
+                            fr[a] = 0.f;
+                        }
+                    }
+                }
+                if (tap != cur_mtap || mgi != cur_mg) {
+                    flush_mask();
+                    cur_mtap = tap;
+                    cur_mg = mgi;
+                    mval = (P.mask != nullptr && pi.valid)
+                               ? __ldg(P.mask + (((int64_t)pi.b * g.mg + mgi) * g.K + tap) * (int64_t)g.P + pi.p)
+                               : 1.f;
+                }
+                // corner geometry of this (position, tap, offset group)
+                int64_t row[NC];
+                float wc[NC];
+                bool okc[NC];
+#pragma unroll
+                for (int c = 0; c < NC; ++c) {
+                    bool v = pi.valid && (deformable || c == 0);
+                    int flat = 0;
+                    float w = 1.f;
+#pragma unroll
+                    for (int a = 0; a < DIM; ++a) {
+                        const int bit = (c >> (DIM - 1 - a)) & 1;
+                        const int i = (int)((unsigned)fl[a] + (unsigned)bit);
+                        v = v && ((unsigned)i < (unsigned)g.img[a]);
+                        flat = flat * g.img[a] + i;
+                        w *= bit ? fr[a] : (1.f - fr[a]);
+                    }
+                    okc[c] = v;
+                    wc[c] = v ? w : 0.f;
+                    row[c] = v ? ((int64_t)pi.b * g.S + flat) * g.Cs : 0;
+                }
+                // this warp's 32 columns of the chunk
+                uint32_t raw[32];
+                ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(lane_q * 32) << 16) + (uint32_t)(q * ncol + ci * 64 + half * 32),
+                                   raw);
+                ptx::tmem_ld_wait();
+                if (pi.valid) {
+                    float gv[32];
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) gv[e] = __uint_as_float(raw[e]);
+                    const int ch0 = chan0 + half * 32;
+                    if (want_coord) {
+                        float dotc[NC];
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) dotc[c] = 0.f;
+#pragma unroll
+                        for (int piece = 0; piece < 32 / PS; ++piece) {
+                            CornerLoad<PS, TI> cl[NC];
+#pragma unroll
+                            for (int c = 0; c < NC; ++c) cl[c].load(img + row[c] + ch0 + piece * PS);
+#pragma unroll
+                            for (int c = 0; c < NC; ++c) dotc[c] += cl[c].dot(gv + piece * PS);
+                        }
+                        float s_val = 0.f;
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) s_val = fmaf(wc[c], dotc[c], s_val);
+                        gm_sum += s_val;
+                        if (P.goff != nullptr) {
+#pragma unroll
+                            for (int a = 0; a < DIM; ++a) {
+                                float ds = 0.f;
+#pragma unroll
+                                for (int c = 0; c < NC; ++c) {
+                                    if (okc[c]) {
+                                        float w = ((c >> (DIM - 1 - a)) & 1) ? 1.f : -1.f;
+#pragma unroll
+                                        for (int a2 = 0; a2 < DIM; ++a2)
+                                            if (a2 != a) w *= ((c >> (DIM - 1 - a2)) & 1) ? fr[a2] : (1.f - fr[a2]);
+                                        ds = fmaf(w, dotc[c], ds);
+                                    }
+                                }
+                                go_sum[a] = fmaf(mval, ds, go_sum[a]);
+                            }
+                        }
+                    }
+                    if (P.img_grad_cl != nullptr) {
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) {
+                            if (okc[c]) {
+                                const float sc = mval * wc[c];
+                                float *dst = P.img_grad_cl + row[c] + ch0;
+#pragma unroll
+                                for (int e = 0; e < 32; e += 4)
+                                    red_add_v4(dst + e, gv[e] * sc, gv[e + 1] * sc, gv[e + 2] * sc, gv[e + 3] * sc);
+                            }
+                        }
+                    }
+                }
+            }
+            // release the accumulator
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&t_empty[q]);
+        }
+        flush_off();
+        flush_mask();
+    } else if (warp == DG_EPI_WARPS) {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t idesc = ptx::instr_desc_f16(MODE == TC_F16 ? 0 : 1, TILE_POS, ncol, 0, 0);
+            bool ok = ptx::mbar_wait(a_full, 0);
+            if (!ok) atomicExch(P.status, 302);
+            const uint32_t a_addr = ptx::smem_u32(sA);
+            int j = 0;  // running B stage counter
+            for (int blk = 0; blk < n_blocks && ok; ++blk) {
+                const int q = blk % NQ;
+                if (!ptx::mbar_wait(&t_empty[q], (uint32_t)(((blk / NQ) & 1) ^ 1))) {
+                    atomicExch(P.status, 303);
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(q * ncol);
+                for (int rc = 0; rc < RC && ok; ++rc, ++j) {
+                    const int s = j % BS;
+                    if (!ptx::mbar_wait(&b_full[s], (uint32_t)((j / BS) & 1))) {
+                        atomicExch(P.status, 304);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t a_rc = a_addr + (uint32_t)(rc * PARTS * DG_A_TILE);
+                    const uint32_t b_addr = ptx::smem_u32(sB + (size_t)s * b_stage_bytes);
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        const uint64_t a_hi = ptx::smem_desc_sw128(a_rc + k4 * 32, 16, 1024);
+                        const uint64_t b_hi = ptx::smem_desc_sw128(b_addr + k4 * 32, 16, 1024);
+                        ptx::mma_f16(d_tmem, a_hi, b_hi, idesc, (rc > 0 || k4 > 0) ? 1u : 0u);
+                        if constexpr (SPLIT) {
+                            const uint64_t a_lo = ptx::smem_desc_sw128(a_rc + DG_A_TILE + k4 * 32, 16, 1024);
+                            const uint64_t b_lo = ptx::smem_desc_sw128(b_addr + b_part_bytes + k4 * 32, 16, 1024);
+                            ptx::mma_f16(d_tmem, a_lo, b_hi, idesc, 1u);
+                            ptx::mma_f16(d_tmem, a_hi, b_lo, idesc, 1u);
+                        }
+                    }
+                    ptx::mma_commit(&b_empty[s]);
+                }
+                if (ok) ptx::mma_commit(&t_full[q]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ TMA: dense tiles once, weight ring
+        if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(a_full, a_bytes);
+            for (int rc = 0; rc < RC; ++rc) {
+                ptx::tma_load_2d(sA + (size_t)(rc * PARTS) * DG_A_TILE, &tmap_a_hi, a_full, grp * g.cdg + rc * 64, (int)m0);
+                if (SPLIT)
+                    ptx::tma_load_2d(sA + (size_t)(rc * PARTS + 1) * DG_A_TILE, &tmap_a_lo, a_full, grp * g.cdg + rc * 64,
+                                     (int)m0);
+            }
+            int j = 0, issued = 0;
+            bool ok = true;
+            for (int blk = 0; blk < n_blocks && ok; ++blk) {
+                const int tap = blk / blocks_per_tap;
+                const int cc0 = (blk % blocks_per_tap) * NB;
+                for (int rc = 0; rc < RC; ++rc, ++j) {
+                    const int s = j % BS;
+                    if (!ptx::mbar_wait(&b_empty[s], (uint32_t)(((j / BS) & 1) ^ 1))) {
+                        atomicExch(P.status, 305);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *dst = sB + (size_t)s * b_stage_bytes;
+                    ptx::mbar_arrive_expect_tx(&b_full[s], b_stage_bytes);
+                    ptx::tma_load_4d(dst, &tmap_b_hi, &b_full[s], rc * 64, cc0 * CHUNK_C, tap, grp);
+                    if (SPLIT) ptx::tma_load_4d(dst + b_part_bytes, &tmap_b_lo, &b_full[s], rc * 64, cc0 * CHUNK_C, tap, grp);
+                    issued = j + 1;
+                }
+            }
+            ptx::mbar_wait(a_full, 0);
+            if (issued > 0) {
+                const int jj = issued - 1;
+                ptx::mbar_wait(&b_full[jj % BS], (uint32_t)((jj / BS) & 1));
+            }
+        }
+        __syncwarp();
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == DG_EPI_WARPS) ptx::tmem_dealloc(tmem_base, DG_TMEM_COLS);
+}
+
+// [B, C, S] f32 -> [B, S, C] bf16 hi + lo
+__global__ void __launch_bounds__(256) to_channels_last_split_kernel(const float *__restrict__ src,
+                                                                     __nv_bfloat16 *__restrict__ hi,
+                                                                     __nv_bfloat16 *__restrict__ lo, int C, int S) {
+    __shared__ float tile[32][33];
+    const int b = blockIdx.z;
+    const int s0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const float *in = src + (int64_t)b * C * S;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = c0 + ty + 8 * i, s = s0 + tx;
+        if (c < C && s < S) tile[ty + 8 * i][tx] = in[(int64_t)c * S + s];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int s = s0 + ty + 8 * i, c = c0 + tx;
+        if (c < C && s < S) {
+            const float v = tile[tx][ty + 8 * i];
+            const __nv_bfloat16 h = __float2bfloat16_rn(v);
+            const int64_t o = (int64_t)b * C * S + (int64_t)s * C + c;
+            hi[o] = h;
+            lo[o] = __float2bfloat16_rn(v - __bfloat162float(h));
+        }
+    }
+}
+
+// [B, S, C] f32 (+ bias[c]) -> [B, C, S] in the destination type
+template <typename TO>
+__global__ void __launch_bounds__(256) from_channels_last_bias_kernel(const float *__restrict__ src,
+                                                                      const float *__restrict__ bias,
+                                                                      TO *__restrict__ dst, int C, int S) {
+    __shared__ float tile[32][33];
+    const int b = blockIdx.z;
+    const int s0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const float *in = src + (int64_t)b * C * S;
+    TO *out = dst + (int64_t)b * C * S;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int s = s0 + ty + 8 * i, c = c0 + tx;
+        if (c < C && s < S) tile[ty + 8 * i][tx] = in[(int64_t)s * C + c];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = c0 + ty + 8 * i, s = s0 + tx;
+        if (c < C && s < S) {
+            float v = tile[tx][ty + 8 * i];
+            if (bias != nullptr) v += __ldg(bias + c);
+            store_acc(out, (int64_t)c * S + s, v);
+        }
+    }
+}
+
+size_t dgrad_smem_bytes(int mode, int rc, int nb, int b_stages) {
+    const int parts = mode == TC_SPLIT ? 2 : 1;
+    return 1024 + (size_t)rc * parts * DG_A_TILE + (size_t)b_stages * parts * nb * 64 * 128 + (1 + 2 * b_stages + 16) * 8 +
+           16;
+}
+
+template <int DIM, int MODE>
+cudaError_t launch_dgrad_t(const DgradParams<DIM> &P, dim3 grid, const CUtensorMap *maps, cudaStream_t stream) {
+    const size_t smem = dgrad_smem_bytes(MODE, P.rc, P.nb, P.b_stages);
+    auto kern = dcn_dgrad_tc_kernel<DIM, MODE>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    LaunchScope scope("dcn_dgrad_tc", stream);
+    kern<<<grid, DG_THREADS, smem, stream>>>(P, maps[0], maps[1], maps[2], maps[3]);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool dgrad_tc_config(int mode, int cdg, int csg, int *nb, int *b_stages) {
+    const int rc = cdg / 64;
+    const int n = ((csg / 64) % 2 == 0) ? 2 : 1;
+    int s = 0;
+    for (int cand = 6; cand >= 2; --cand)
+        if (dgrad_smem_bytes(mode, rc, n, cand) <= 227 * 1024) { s = cand; break; }
+    if (s == 0) return false;
+    *nb = n;
+    *b_stages = s;
+    return true;
+}
+
+cudaError_t launch_to_channels_last_split(const float *src, void *hi, void *lo, int B, int C, int S,
+                                          cudaStream_t stream) {
+    dim3 grid((S + 31) / 32, (C + 31) / 32, B);
+    LaunchScope scope("to_channels_last", stream);
+    to_channels_last_split_kernel<<<grid, 256, 0, stream>>>(src, (__nv_bfloat16 *)hi, (__nv_bfloat16 *)lo, C, S);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_from_channels_last_bias(const float *src, const float *bias, void *dst, int dst_dtype, int B, int C,
+                                           int S, cudaStream_t stream) {
+    dim3 grid((S + 31) / 32, (C + 31) / 32, B);
+    LaunchScope scope("from_channels_last", stream);
+    if (dst_dtype == DT_F32)
+        from_channels_last_bias_kernel<float><<<grid, 256, 0, stream>>>(src, bias, (float *)dst, C, S);
+    else if (dst_dtype == DT_BF16)
+        from_channels_last_bias_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(src, bias, (__nv_bfloat16 *)dst, C, S);
+    else if (dst_dtype == DT_F16)
+        from_channels_last_bias_kernel<__half><<<grid, 256, 0, stream>>>(src, bias, (__half *)dst, C, S);
+    else
+        return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+// dense_cl_*: dense tensor channels-last [B*P, Cd] 16-bit (hi / lo); w_kd_*: weights packed [g][tap][s'][d'];
+// img_cl: sampled image channels-last (needed for goff / gmask); accumulation targets are f32 and
+// initialised by the caller.
+cudaError_t launch_gemm_scatter_tc(const GeoHost &h, int mode, const void *dense_cl_hi, const void *dense_cl_lo,
+                                   const void *w_kd_hi, const void *w_kd_lo, const void *img_cl, const float *offset,
+                                   const float *mask, float *img_grad_cl, float *goff, float *gmask, int *status,
+                                   cudaStream_t stream) {
+    const int cdg = h.Cd / h.groups, csg = h.Cs / h.groups;
+    int nb = 0, bs = 0;
+    if (!dgrad_tc_config(mode, cdg, csg, &nb, &bs)) return cudaErrorInvalidConfiguration;
+    const long long BP = (long long)h.B * h.P;
+    CUtensorMap maps[4];
+    {
+        const uint64_t dims[2] = {(uint64_t)h.Cd, (uint64_t)BP};
+        const uint64_t strides[1] = {(uint64_t)h.Cd * 2};
+        const uint32_t box[2] = {64, TILE_POS};
+        if (!make_tensor_map_16bit(&maps[0], dense_cl_hi, 2, dims, strides, box)) return cudaErrorInvalidValue;
+        if (mode == TC_SPLIT) {
+            if (!make_tensor_map_16bit(&maps[1], dense_cl_lo, 2, dims, strides, box)) return cudaErrorInvalidValue;
+        } else {
+            maps[1] = maps[0];
+        }
+    }
+    {
+        const uint64_t dims[4] = {(uint64_t)cdg, (uint64_t)csg, (uint64_t)h.K, (uint64_t)h.groups};
+        const uint64_t strides[3] = {(uint64_t)cdg * 2, (uint64_t)cdg * csg * 2, (uint64_t)cdg * csg * h.K * 2};
+        const uint32_t box[4] = {64, (uint32_t)(nb * 64), 1, 1};
+        if (!make_tensor_map_16bit(&maps[2], w_kd_hi, 4, dims, strides, box)) return cudaErrorInvalidValue;
+        if (mode == TC_SPLIT) {
+            if (!make_tensor_map_16bit(&maps[3], w_kd_lo, 4, dims, strides, box)) return cudaErrorInvalidValue;
+        } else {
+            maps[3] = maps[2];
+        }
+    }
+    dim3 grid((unsigned)((BP + TILE_POS - 1) / TILE_POS), (unsigned)h.groups);
+    auto run = [&](auto dimc) -> cudaError_t {
+        constexpr int DIM = decltype(dimc)::value;
+        DgradParams<DIM> P;
+        P.g = geo_from_host<DIM>(h);
+        P.img_cl = img_cl;
+        P.offset = offset;
+        P.mask = mask;
+        P.img_grad_cl = img_grad_cl;
+        P.goff = goff;
+        P.gmask = gmask;
+        P.status = status;
+        P.nb = nb;
+        P.rc = cdg / 64;
+        P.b_stages = bs;
+        P.chunks_per_tap = csg / CHUNK_C;
+        if (mode == TC_BF16) return launch_dgrad_t<DIM, TC_BF16>(P, grid, maps, stream);
+        if (mode == TC_F16) return launch_dgrad_t<DIM, TC_F16>(P, grid, maps, stream);
+        return launch_dgrad_t<DIM, TC_SPLIT>(P, grid, maps, stream);
+    };
+    if (h.dim == 1) return run(std::integral_constant<int, 1>());
+    if (h.dim == 2) return run(std::integral_constant<int, 2>());
+    if (h.dim == 3) return run(std::integral_constant<int, 3>());
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace tvdcn_b200

@@ -4,17 +4,18 @@
 //
 // It is an implicit GEMM  D[128 positions x BN dense channels] += A[128 x 64] * B[BN x 64]^T  over K chunks
 // of 64 channels of one kernel tap.  The A tile (the im2col columns of the reference,
-// tvdcn/csrc/ops/cuda/deform_conv2d_common_kernels.cu:138-192) is never written to global memory: four
+// tvdcn/csrc/ops/cuda/deform_conv2d_common_kernels.cu:138-192) is never written to global memory: eight
 // producer warps sample a channels-last copy of the image straight into the 128-byte-swizzled shared
 // memory layout the tensor core reads.  The B tile (weights packed per tap) arrives by TMA.  One thread
 // issues tcgen05.mma with the accumulator in tensor memory; the producer warps then read it back
 // (tcgen05.ld: lane = position) and store NCHW with the bias added, so the reference's output_buf
 // transpose and bias pass (tvdcn/csrc/ops/cuda/deform_conv2d_kernel.cpp:371-380) are gone too.
 //
-// Warp roles (192 threads): warps 0-3 producers + epilogue, warp 4 MMA issue + TMEM owner, warp 5 TMA.
+// Warp roles (320 threads): warps 0-7 producers + epilogue, warp 8 MMA issue + TMEM owner, warp 9 TMA.
 #include <algorithm>
 #include <type_traits>
 
+#include "plan.h"
 #include "sm100_common.cuh"
 
 namespace tvdcn_b200 {
@@ -35,11 +36,12 @@ struct FwdParams {
 
 namespace {
 
-constexpr int FWD_THREADS = 192;
-constexpr int PRODUCERS = 128;
+constexpr int PRODUCER_WARPS = 8;
+constexpr int PRODUCERS = PRODUCER_WARPS * 32;
+constexpr int FWD_THREADS = PRODUCERS + 64;
 
 template <int DIM, int MODE>
-__global__ void __launch_bounds__(FWD_THREADS, 2)
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tmap_hi,
                   const __grid_constant__ CUtensorMap tmap_lo) {
     constexpr int NC = 1 << DIM;
@@ -76,18 +78,18 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            ptx::mbar_init(&full_a[s], 4);
+            ptx::mbar_init(&full_a[s], PRODUCER_WARPS);
             ptx::mbar_init(&full_b[s], 1);
             ptx::mbar_init(&empty[s], 1);
         }
         ptx::mbar_init(accum, 1);
         ptx::fence_mbar_init();
     }
-    if (warp == 5 && lane == 0) {
+    if (warp == PRODUCER_WARPS + 1 && lane == 0) {
         ptx::prefetch_tmap(&tmap_hi);
         if (SPLIT) ptx::prefetch_tmap(&tmap_lo);
     }
-    if (warp == 4) {
+    if (warp == PRODUCER_WARPS) {
         ptx::tmem_alloc(tmem_slot, ncols);
         ptx::tmem_relinquish();
     }
@@ -96,10 +98,12 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < 4) {
+    if (warp < PRODUCER_WARPS) {
         // ------------------------------------------------------------------ producers
         const int t = threadIdx.x;
-        const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + t);
+        // position this thread plans for (threads 0..127) and stores in the epilogue (TMEM lane of its warp)
+        const int my_pos = (warp & 3) * 32 + lane;
+        const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + my_pos);
         int cur_tap = -1, cur_og = -1, cur_mg = -1, pb = 1;
         bool ok = true;
         // A failed wait never leaves the loop early: every producer keeps taking part in the named barrier
@@ -112,10 +116,12 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
             const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
             if (tap != cur_tap || ogi != cur_og || mgi != cur_mg) {
                 pb ^= 1;
-                PlanView<DIM> pv{plan_rows + pb * NC * TILE_POS, plan_wts + pb * NC * TILE_POS};
-                fill_plan<DIM>(g, pi, P.offset, P.mask, tap, ogi, mgi, t, pv);
+                if (t < TILE_POS) {
+                    PlanView<DIM> pv{plan_rows + pb * NC * TILE_POS, plan_wts + pb * NC * TILE_POS};
+                    fill_plan<DIM>(g, pi, P.offset, P.mask, tap, ogi, mgi, t, TILE_POS, pv);
+                }
                 cur_tap = tap; cur_og = ogi; cur_mg = mgi;
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 256;" ::: "memory");
             }
             const int *rows = plan_rows + pb * NC * TILE_POS;
             const float *wts = plan_wts + pb * NC * TILE_POS;
@@ -126,72 +132,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
             ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the __syncwarp below
             if (!ok) continue;
             uint8_t *a_hi = sA + (size_t)s * a_stage_bytes;
-            if constexpr (!SPLIT) {
-                const T16 *img = reinterpret_cast<const T16 *>(P.img_cl);
-                const int oct = t & 7;
-#pragma unroll 2
-                for (int it = 0; it < 8; ++it) {
-                    const int pos = it * 16 + (t >> 3);
-                    float acc[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-#pragma unroll
-                    for (int c = 0; c < NC; ++c) {
-                        const float w = wts[c * TILE_POS + pos];
-                        if (w != 0.f) {
-                            const int row = rows[c * TILE_POS + pos];
-                            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(
-                                img + (int64_t)row * g.Cs + chan0 + oct * 8));
-                            float f[8];
-                            unpack8(v, f, T16());
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, f[e], acc[e]);
-                        }
-                    }
-                    uint4 o;
-                    o.x = pack2(acc[0], acc[1], T16());
-                    o.y = pack2(acc[2], acc[3], T16());
-                    o.z = pack2(acc[4], acc[5], T16());
-                    o.w = pack2(acc[6], acc[7], T16());
-                    *reinterpret_cast<uint4 *>(a_hi + sw128_offset(pos, oct)) = o;
-                }
-            } else {
-                const float *img = reinterpret_cast<const float *>(P.img_cl);
-                uint8_t *a_lo = a_hi + A_TILE_BYTES;
-                const int quad = t & 15;
-#pragma unroll 2
-                for (int it = 0; it < 16; ++it) {
-                    const int pos = it * 8 + (t >> 4);
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int c = 0; c < NC; ++c) {
-                        const float w = wts[c * TILE_POS + pos];
-                        if (w != 0.f) {
-                            const int row = rows[c * TILE_POS + pos];
-                            const float4 v = __ldg(reinterpret_cast<const float4 *>(
-                                img + (int64_t)row * g.Cs + chan0 + quad * 4));
-                            acc[0] = fmaf(w, v.x, acc[0]);
-                            acc[1] = fmaf(w, v.y, acc[1]);
-                            acc[2] = fmaf(w, v.z, acc[2]);
-                            acc[3] = fmaf(w, v.w, acc[3]);
-                        }
-                    }
-                    float hi[4], lo[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        hi[e] = __bfloat162float(__float2bfloat16_rn(acc[e]));
-                        lo[e] = acc[e] - hi[e];
-                    }
-                    uint2 oh, ol;
-                    oh.x = pack2(hi[0], hi[1], __nv_bfloat16());
-                    oh.y = pack2(hi[2], hi[3], __nv_bfloat16());
-                    ol.x = pack2(lo[0], lo[1], __nv_bfloat16());
-                    ol.y = pack2(lo[2], lo[3], __nv_bfloat16());
-                    const uint32_t off = sw128_offset(pos, quad >> 1) + (uint32_t)(quad & 1) * 8u;
-                    *reinterpret_cast<uint2 *>(a_hi + off) = oh;
-                    *reinterpret_cast<uint2 *>(a_lo + off) = ol;
-                }
-            }
+            produce_tile<NC, MODE, PRODUCERS>(a_hi, a_hi + A_TILE_BYTES, P.img_cl, g.Cs, chan0, rows, wts, TILE_POS, TILE_POS, t);
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&full_a[s]);
@@ -205,8 +146,10 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
         ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is a whole-warp instruction
         ptx::tc_fence_after();
         if (ok) {
-            const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-            for (int cb = 0; cb < BN / 32; ++cb) {
+            // warps w and w + 4 share TMEM lanes 32 * (w % 4) ...; they split the columns
+            const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+            const int blocks = BN / 32;
+            for (int cb = (warp >> 2); cb < blocks; cb += 2) {
                 uint32_t v[32];
                 ptx::tmem_ld_32x32(lane_base + (uint32_t)(cb * 32), v);
                 ptx::tmem_ld_wait();
@@ -225,7 +168,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                 }
             }
         }
-    } else if (warp == 4) {
+    } else if (warp == PRODUCER_WARPS) {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
             const uint32_t idesc = ptx::instr_desc_f16(MODE == TC_F16 ? 0 : 1, TILE_POS, BN, 0, 0);
@@ -285,7 +228,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
 
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == 4) ptx::tmem_dealloc(tmem_base, ncols);
+    if (warp == PRODUCER_WARPS) ptx::tmem_dealloc(tmem_base, ncols);
 }
 
 // ---- staging kernels ---------------------------------------------------------------------------------
@@ -387,6 +330,17 @@ cudaError_t launch_pack_weight(const void *w, int dtype, int mode, int groups, i
     return cudaGetLastError();
 }
 
+// f32 -> bf16 hi + lo (same layout), for operands that reach the tensor core through TMA
+__global__ void split_f32_kernel(const float *__restrict__ src, __nv_bfloat16 *__restrict__ hi,
+                                 __nv_bfloat16 *__restrict__ lo, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = src[i];
+        const __nv_bfloat16 h = __float2bfloat16_rn(v);
+        hi[i] = h;
+        lo[i] = __float2bfloat16_rn(v - __bfloat162float(h));
+    }
+}
+
 }  // namespace
 
 cudaError_t launch_pack_weight_ks(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
@@ -396,6 +350,13 @@ cudaError_t launch_pack_weight_ks(const void *w, int dtype, int mode, int groups
 cudaError_t launch_pack_weight_kd(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
                                   void *lo, cudaStream_t stream) {
     return launch_pack_weight<false>(w, dtype, mode, groups, cdg, csg, K, hi, lo, stream);
+}
+
+cudaError_t launch_split_f32(const float *src, void *hi, void *lo, int64_t n, cudaStream_t stream) {
+    const int blocks = (int)std::min<int64_t>((n + 255) / 256, 148 * 16);
+    LaunchScope scope("split_f32", stream);
+    split_f32_kernel<<<blocks, 256, 0, stream>>>(src, (__nv_bfloat16 *)hi, (__nv_bfloat16 *)lo, n);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_to_channels_last(const void *src, void *dst, int B, int C, int S, int elem_bytes,
@@ -463,16 +424,9 @@ bool fwd_tc_config(int dim, int mode, int cdg, int *bn, int *stages) {
     for (int cand : {256, 128, 64})
         if (cand <= cap && cdg % cand == 0) { n = cand; break; }
     if (n == 0) return false;
-    // two CTAs per SM (so one tile's epilogue overlaps another's main loop) when at least 3 stages fit in
-    // half of the 227 KB; otherwise one CTA with as many stages as fit, at most 6
     int s = 0;
-    for (int cand = 6; cand >= 2; --cand)
-        if (fwd_tc_smem_bytes(dim, mode, n, cand) <= 113 * 1024) { s = cand; break; }
-    if (s < 3) {
-        s = 0;
-        for (int cand = 6; cand >= 2; --cand)
-            if (fwd_tc_smem_bytes(dim, mode, n, cand) <= 227 * 1024) { s = cand; break; }
-    }
+    for (int cand = 4; cand >= 2; --cand)
+        if (fwd_tc_smem_bytes(dim, mode, n, cand) <= 227 * 1024) { s = cand; break; }
     if (s == 0) return false;
     *bn = n;
     *stages = s;
@@ -491,23 +445,6 @@ cudaError_t launch_fwd_tc_t(const GeoHost &h, const FwdParams<DIM> &P, const CUt
     LaunchScope scope("dcn_fwd_tc", stream);
     kern<<<grid, FWD_THREADS, smem, stream>>>(P, hi, lo);
     return cudaGetLastError();
-}
-
-template <int DIM>
-Geo<DIM> geo_from_host(const GeoHost &h) {
-    Geo<DIM> g;
-    g.B = h.B; g.Cs = h.Cs; g.Cd = h.Cd; g.groups = h.groups; g.og = h.og; g.mg = h.mg; g.K = h.K;
-    g.S = h.S; g.P = h.P;
-    g.csg = h.Cs / h.groups;
-    g.cdg = h.Cd / h.groups;
-    g.cs_per_og = h.og > 0 ? h.Cs / h.og : h.Cs;
-    g.cs_per_mg = h.mg > 0 ? h.Cs / h.mg : h.Cs;
-    g.BP = (long long)h.B * h.P;
-    for (int a = 0; a < DIM; ++a) {
-        g.img[a] = h.img[a]; g.grid[a] = h.grid[a]; g.ker[a] = h.ker[a];
-        g.stride[a] = h.stride[a]; g.pad[a] = h.pad[a]; g.dil[a] = h.dil[a];
-    }
-    return g;
 }
 
 // img_cl: channels-last sampled image (16-bit or f32 per mode); w_hi / w_lo: weights packed [g][tap][d'][s'].

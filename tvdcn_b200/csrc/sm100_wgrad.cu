@@ -1,0 +1,364 @@
+// Tensor-core weight gradient with on-the-fly sampling (tcgen05 / TMEM).
+//
+//   gw[d, s', tap] += sum_{b, p} dense[b, d, p] * mask * sample(img[b, s], pos(b, og(s), tap, p))
+//
+// Replaces the second im2col + addmm_ of the reference's backward loop
+// (tvdcn/csrc/ops/cuda/deform_conv2d_kernel.cpp:600-626): the sampled columns never reach global memory.
+//
+// GEMM view: D[dense channel d (M) x column k = (tap, channel) (N)] += A[d x pos] * B[pos x k], reduction
+// over grid positions.  One CTA owns up to 2 x 128 dense channels and up to 4 x 64 columns (the whole
+// accumulator lives in tensor memory, up to 512 columns) and walks a range of 64-position chunks:
+//   A = dense^T tile [128 d][64 pos]: position-contiguous in the NCHW tensor, so it is a K-major operand
+//       that TMA loads directly (zero-filled past the end of an image);
+//   B = sampled tile [64 pos][64 channels] per column block, written by the producer warps in the same
+//       swizzled row = position layout as the forward kernel and consumed as an MN-major operand.
+// Position ranges are split over CTAs; partial results are added to gw (f32) with atomics.
+//
+// Warp roles (320 threads): warps 0-7 producers + epilogue, warp 8 MMA issue + TMEM owner, warp 9 TMA.
+#include <algorithm>
+#include <type_traits>
+
+#include "plan.h"
+#include "sm100_common.cuh"
+
+namespace tvdcn_b200 {
+
+template <int DIM>
+struct WgradParams {
+    Geo<DIM> g;
+    const void *img_cl;
+    const float *offset;
+    const float *mask;
+    float *gw;               // [Cd, csg, K] f32, accumulated into
+    int *status;
+    int stages;
+    int chunks_per_tap;      // csg / 64
+    int n_sub;               // 64-column blocks per CTA
+    int m_tiles;             // 128-dense-channel tiles per CTA
+    int chunks_per_image;    // ceil(P / 64)
+    int chunks_per_split;
+    int total_chunks;        // B * chunks_per_image
+};
+
+namespace {
+
+constexpr int WG_PRODUCER_WARPS = 8;
+constexpr int WG_PRODUCERS = WG_PRODUCER_WARPS * 32;
+constexpr int WG_THREADS = WG_PRODUCERS + 64;
+constexpr int WG_POS = 64;                       // positions per stage
+constexpr int WG_A_TILE = 128 * 128;             // [128 d][64 pos] 16-bit
+constexpr int WG_B_TILE = WG_POS * 128;          // [64 pos][64 ch] 16-bit
+
+template <int DIM, int MODE>
+__global__ void __launch_bounds__(WG_THREADS, 1)
+dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMap tmap_hi,
+                    const __grid_constant__ CUtensorMap tmap_lo) {
+    constexpr int NC = 1 << DIM;
+    constexpr bool SPLIT = MODE == TC_SPLIT;
+    constexpr int PARTS = SPLIT ? 2 : 1;
+    const Geo<DIM> &g = P.g;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int S = P.stages;
+    const int NS = P.n_sub, MT = P.m_tiles;
+    const uint32_t a_stage_bytes = (uint32_t)(MT * PARTS * WG_A_TILE);   // [m][part]
+    const uint32_t b_part_bytes = (uint32_t)(NS * WG_B_TILE);            // [part][sub]
+    const uint32_t b_stage_bytes = b_part_bytes * PARTS;
+    uint8_t *sA = smem;
+    uint8_t *sB = sA + (size_t)S * a_stage_bytes;
+    int *plan_rows = reinterpret_cast<int *>(sB + (size_t)S * b_stage_bytes);   // [2][NS][NC][64]
+    float *plan_wts = reinterpret_cast<float *>(plan_rows + 2 * NS * NC * WG_POS);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(plan_wts + 2 * NS * NC * WG_POS);
+    uint64_t *full_s = bars;           // sampled tiles written
+    uint64_t *full_d = bars + S;       // dense tiles landed
+    uint64_t *empty = bars + 2 * S;
+    uint64_t *accum = bars + 3 * S;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub_total = g.K * P.chunks_per_tap;                 // 64-column blocks per group
+    const int kt0 = blockIdx.x * NS;                              // first column block of this CTA
+    const int y_tiles = (g.cdg + 128 * MT - 1) / (128 * MT);
+    const int grp = blockIdx.y / y_tiles;
+    const int d0 = (blockIdx.y % y_tiles) * 128 * MT;             // first dense channel within the group
+    const int chunk_begin = blockIdx.z * P.chunks_per_split;
+    const int chunk_end = min(chunk_begin + P.chunks_per_split, P.total_chunks);
+    const int n_stages = max(chunk_end - chunk_begin, 0);
+    const uint32_t cols_used = (uint32_t)(MT * NS * 64);
+    uint32_t ncols = 32;
+    while (ncols < cols_used) ncols <<= 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            ptx::mbar_init(&full_s[s], WG_PRODUCER_WARPS);
+            ptx::mbar_init(&full_d[s], 1);
+            ptx::mbar_init(&empty[s], 1);
+        }
+        ptx::mbar_init(accum, 1);
+        ptx::fence_mbar_init();
+    }
+    if (warp == WG_PRODUCER_WARPS + 1 && lane == 0) {
+        ptx::prefetch_tmap(&tmap_hi);
+        if (SPLIT) ptx::prefetch_tmap(&tmap_lo);
+    }
+    if (warp == WG_PRODUCER_WARPS) {
+        ptx::tmem_alloc(tmem_slot, ncols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < WG_PRODUCER_WARPS) {
+        // ------------------------------------------------------------------ producers
+        const int t = threadIdx.x;
+        const int my_sub = t / WG_POS, my_slot = t % WG_POS;     // plan entry this thread fills
+        const int my_kt = kt0 + my_sub;
+        const bool my_sub_ok = my_sub < NS && my_kt < sub_total;
+        const int my_tap = my_sub_ok ? my_kt / P.chunks_per_tap : 0;
+        const int my_chan0 = grp * g.csg + (my_sub_ok ? my_kt % P.chunks_per_tap : 0) * CHUNK_C;
+        const int my_og = g.og > 0 ? my_chan0 / g.cs_per_og : 0;
+        const int my_mg = g.mg > 0 ? my_chan0 / g.cs_per_mg : 0;
+        bool ok = true;
+        for (int i = 0; i < n_stages; ++i) {
+            const int s = i % S, r = i / S;
+            const int pc = chunk_begin + i;
+            const int b = pc / P.chunks_per_image;
+            const int p0 = (pc % P.chunks_per_image) * WG_POS;
+            const int pb = i & 1;
+            if (my_sub < NS) {
+                PosInfo<DIM> pi;
+                const int p = p0 + my_slot;
+                pi.valid = my_sub_ok && p < g.P;
+                pi.b = b;
+                pi.p = pi.valid ? p : 0;
+                int rem = pi.p;
+#pragma unroll
+                for (int a = DIM - 1; a >= 0; --a) {
+                    const int c = rem % g.grid[a];
+                    rem /= g.grid[a];
+                    pi.base[a] = c * g.stride[a] - g.pad[a];
+                }
+                PlanView<DIM> pv{plan_rows + (pb * NS + my_sub) * NC * WG_POS,
+                                 plan_wts + (pb * NS + my_sub) * NC * WG_POS};
+                fill_plan<DIM>(g, pi, P.offset, P.mask, my_tap, my_og, my_mg, my_slot, WG_POS, pv);
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (ok && !ptx::mbar_wait(&empty[s], (uint32_t)((r & 1) ^ 1))) {
+                atomicExch(P.status, 201);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) continue;
+            uint8_t *b_hi = sB + (size_t)s * b_stage_bytes;
+            for (int sub = 0; sub < NS; ++sub) {
+                const int kt = kt0 + sub;
+                const int chan0 = grp * g.csg + (kt < sub_total ? kt % P.chunks_per_tap : 0) * CHUNK_C;
+                produce_tile<NC, MODE, WG_PRODUCERS>(b_hi + sub * WG_B_TILE, b_hi + b_part_bytes + sub * WG_B_TILE,
+                                                     P.img_cl, g.Cs, chan0,
+                                                     plan_rows + (pb * NS + sub) * NC * WG_POS,
+                                                     plan_wts + (pb * NS + sub) * NC * WG_POS, WG_POS, WG_POS, t);
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&full_s[s]);
+        }
+
+        // ------------------------------------------------------------------ epilogue: atomics into gw
+        if (n_stages > 0) {
+            if (ok && !ptx::mbar_wait(accum, 0)) {
+                atomicExch(P.status, 202);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            ptx::tc_fence_after();
+            if (ok) {
+                const int lane_q = warp & 3;
+                const uint32_t lane_base = tmem_base + ((uint32_t)(lane_q * 32) << 16);
+                const int blocks = MT * NS * 2;  // 32-column blocks
+                for (int cb = (warp >> 2); cb < blocks; cb += 2) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32(lane_base + (uint32_t)(cb * 32), v);
+                    ptx::tmem_ld_wait();
+                    const int m = cb / (NS * 2);
+                    const int col0 = (cb % (NS * 2)) * 32;      // column within the M tile
+                    const int sub = col0 / 64;
+                    const int kt = kt0 + sub;
+                    const int dl = d0 + m * 128 + lane_q * 32 + lane;   // dense channel within the group
+                    if (kt < sub_total && dl < g.cdg) {
+                        const int tap = kt / P.chunks_per_tap;
+                        const int sl0 = (kt % P.chunks_per_tap) * CHUNK_C + (col0 % 64);
+                        float *dst = P.gw + ((int64_t)(grp * g.cdg + dl) * g.csg + sl0) * g.K + tap;
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) atomicAdd(dst + (int64_t)e * g.K, __uint_as_float(v[e]));
+                    }
+                }
+            }
+        }
+    } else if (warp == WG_PRODUCER_WARPS) {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t idesc = ptx::instr_desc_f16(MODE == TC_F16 ? 0 : 1, 128, NS * 64, 0, 1);
+            bool ok = true;
+            for (int i = 0; i < n_stages && ok; ++i) {
+                const int s = i % S, r = i / S;
+                if (!ptx::mbar_wait(&full_s[s], (uint32_t)(r & 1)) || !ptx::mbar_wait(&full_d[s], (uint32_t)(r & 1))) {
+                    atomicExch(P.status, 203);
+                    ok = false;
+                    break;
+                }
+                ptx::tc_fence_after();
+                const uint32_t a_addr = ptx::smem_u32(sA + (size_t)s * a_stage_bytes);
+                const uint32_t b_addr = ptx::smem_u32(sB + (size_t)s * b_stage_bytes);
+                for (int m = 0; m < MT; ++m) {
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(m * NS * 64);
+                    const uint32_t am = a_addr + (uint32_t)(m * PARTS * WG_A_TILE);
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4) {
+                        // A: K-major rows of 64 positions; B: MN-major, 16 positions = 16 rows of 128 bytes
+                        const uint64_t a_hi = ptx::smem_desc_sw128(am + k4 * 32, 16, 1024);
+                        const uint64_t b_hi = ptx::smem_desc_sw128(b_addr + k4 * 2048, WG_B_TILE, 1024);
+                        ptx::mma_f16(d_tmem, a_hi, b_hi, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+                        if constexpr (SPLIT) {
+                            const uint64_t a_lo = ptx::smem_desc_sw128(am + WG_A_TILE + k4 * 32, 16, 1024);
+                            const uint64_t b_lo = ptx::smem_desc_sw128(b_addr + b_part_bytes + k4 * 2048, WG_B_TILE, 1024);
+                            ptx::mma_f16(d_tmem, a_lo, b_hi, idesc, 1u);
+                            ptx::mma_f16(d_tmem, a_hi, b_lo, idesc, 1u);
+                        }
+                    }
+                }
+                ptx::mma_commit(&empty[s]);
+            }
+            if (ok && n_stages > 0) ptx::mma_commit(accum);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ TMA: dense tiles
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < n_stages; ++i) {
+                const int s = i % S, r = i / S;
+                if (!ptx::mbar_wait(&empty[s], (uint32_t)((r & 1) ^ 1))) {
+                    atomicExch(P.status, 204);
+                    break;
+                }
+                const int pc = chunk_begin + i;
+                const int b = pc / P.chunks_per_image;
+                const int p0 = (pc % P.chunks_per_image) * WG_POS;
+                uint8_t *a_dst = sA + (size_t)s * a_stage_bytes;
+                ptx::mbar_arrive_expect_tx(&full_d[s], a_stage_bytes);
+                for (int m = 0; m < MT; ++m) {
+                    const int dch = grp * g.cdg + d0 + m * 128;
+                    ptx::tma_load_3d(a_dst + (size_t)(m * PARTS) * WG_A_TILE, &tmap_hi, &full_d[s], p0, dch, b);
+                    if (SPLIT)
+                        ptx::tma_load_3d(a_dst + (size_t)(m * PARTS + 1) * WG_A_TILE, &tmap_lo, &full_d[s], p0, dch, b);
+                }
+                issued = i + 1;
+            }
+            if (issued > 0) {
+                const int i = issued - 1;
+                ptx::mbar_wait(&full_d[i % S], (uint32_t)((i / S) & 1));
+            }
+        }
+        __syncwarp();
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == WG_PRODUCER_WARPS) ptx::tmem_dealloc(tmem_base, ncols);
+}
+
+size_t wgrad_smem_bytes(int dim, int mode, int n_sub, int m_tiles, int stages) {
+    const int parts = mode == TC_SPLIT ? 2 : 1;
+    const size_t stage = (size_t)parts * (m_tiles * WG_A_TILE + n_sub * WG_B_TILE);
+    const size_t plan = (size_t)2 * n_sub * (1 << dim) * WG_POS * 8;
+    return 1024 + stages * stage + plan + (3 * stages + 1) * 8 + 16;
+}
+
+template <int DIM, int MODE>
+cudaError_t launch_wgrad_t(const WgradParams<DIM> &P, dim3 grid, const CUtensorMap &hi, const CUtensorMap &lo,
+                           cudaStream_t stream) {
+    const size_t smem = wgrad_smem_bytes(DIM, MODE, P.n_sub, P.m_tiles, P.stages);
+    auto kern = dcn_wgrad_tc_kernel<DIM, MODE>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    LaunchScope scope("dcn_wgrad_tc", stream);
+    kern<<<grid, WG_THREADS, smem, stream>>>(P, hi, lo);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+// Tile shape and pipeline depth; false when the shape is not covered.
+bool wgrad_tc_config(int dim, int mode, int cdg, int P, int *n_sub, int *m_tiles, int *stages) {
+    if (P % 8 != 0) return false;  // the dense tensor's row pitch must be a multiple of 16 bytes for TMA
+    const int mt = cdg > 128 ? 2 : 1;
+    int ns = mode == TC_SPLIT ? 2 : 4;
+    if (dim == 3 && mode != TC_SPLIT) ns = 4;
+    int s = 0;
+    for (int cand = 4; cand >= 2; --cand)
+        if (wgrad_smem_bytes(dim, mode, ns, mt, cand) <= 227 * 1024) { s = cand; break; }
+    if (s == 0) return false;
+    *n_sub = ns;
+    *m_tiles = mt;
+    *stages = s;
+    return true;
+}
+
+// dense_hi / dense_lo: the dense tensor [B, Cd, P] as 16-bit (the tensor itself for 16-bit data; bf16 hi
+// and lo parts of the f32 tensor in split mode).  gw must be zero-initialised f32.
+cudaError_t launch_sample_wgrad_tc(const GeoHost &h, int mode, const void *dense_hi, const void *dense_lo,
+                                   const void *img_cl, const float *offset, const float *mask, float *gw,
+                                   int *status, cudaStream_t stream) {
+    const int cdg = h.Cd / h.groups, csg = h.Cs / h.groups;
+    int ns = 0, mt = 0, st = 0;
+    if (!wgrad_tc_config(h.dim, mode, cdg, h.P, &ns, &mt, &st)) return cudaErrorInvalidConfiguration;
+    CUtensorMap hi, lo;
+    const uint64_t dims[3] = {(uint64_t)h.P, (uint64_t)h.Cd, (uint64_t)h.B};
+    const uint64_t strides[2] = {(uint64_t)h.P * 2, (uint64_t)h.P * h.Cd * 2};
+    const uint32_t box[3] = {WG_POS, 128, 1};
+    if (!make_tensor_map_16bit(&hi, dense_hi, 3, dims, strides, box)) return cudaErrorInvalidValue;
+    if (mode == TC_SPLIT) {
+        if (!make_tensor_map_16bit(&lo, dense_lo, 3, dims, strides, box)) return cudaErrorInvalidValue;
+    } else {
+        lo = hi;
+    }
+    const int sub_total = h.K * (csg / CHUNK_C);
+    const int k_tiles = (sub_total + ns - 1) / ns;
+    const int y_tiles = h.groups * ((cdg + 128 * mt - 1) / (128 * mt));
+    const int cpi = (h.P + WG_POS - 1) / WG_POS;
+    const int total = h.B * cpi;
+    int splits = std::max(1, 148 / std::max(1, k_tiles * y_tiles));
+    splits = std::min(splits, total);
+    const int per = (total + splits - 1) / splits;
+    splits = (total + per - 1) / per;
+    dim3 grid((unsigned)k_tiles, (unsigned)y_tiles, (unsigned)splits);
+    auto run = [&](auto dimc) -> cudaError_t {
+        constexpr int DIM = decltype(dimc)::value;
+        WgradParams<DIM> P;
+        P.g = geo_from_host<DIM>(h);
+        P.img_cl = img_cl;
+        P.offset = offset;
+        P.mask = mask;
+        P.gw = gw;
+        P.status = status;
+        P.stages = st;
+        P.chunks_per_tap = csg / CHUNK_C;
+        P.n_sub = ns;
+        P.m_tiles = mt;
+        P.chunks_per_image = cpi;
+        P.chunks_per_split = per;
+        P.total_chunks = total;
+        if (mode == TC_BF16) return launch_wgrad_t<DIM, TC_BF16>(P, grid, hi, lo, stream);
+        if (mode == TC_F16) return launch_wgrad_t<DIM, TC_F16>(P, grid, hi, lo, stream);
+        return launch_wgrad_t<DIM, TC_SPLIT>(P, grid, hi, lo, stream);
+    };
+    if (h.dim == 1) return run(std::integral_constant<int, 1>());
+    if (h.dim == 2) return run(std::integral_constant<int, 2>());
+    if (h.dim == 3) return run(std::integral_constant<int, 3>());
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace tvdcn_b200
