@@ -145,6 +145,8 @@ def run_cabi(case: Case, x, w, off, mask, bias, go, engine: int = 0, poison: boo
     for t in (off, mask, bias):
         if t is not None:
             aux = t.dtype
+    if aux is None and x.dtype in (torch.float16, torch.bfloat16):
+        aux = torch.float32  # no offset / mask / bias: nothing constrains it, and f32 keeps the tensor path open
     p = cabi_problem(case, x.dtype, aux, engine)
     dev = x.device
     stream = torch.cuda.current_stream(dev).cuda_stream

@@ -121,6 +121,7 @@ Call prepare(const Tensor &input, const Tensor &weight, const OptTensor &offset,
     if (deformable) check_aux(*offset, "offset");
     if (modulated) check_aux(*mask, "mask");
     if (with_bias) check_aux(*bias, "bias");
+    if (!aux_set && low) aux = at::kFloat;  // nothing constrains it; f32 keeps the tensor-core kernels eligible
 
     c.input = input.contiguous();
     c.weight = weight.contiguous();
