@@ -115,6 +115,33 @@ int tvdcn_b200_deform_conv_forward(const tvdcn_problem *p,
                                    void *cuda_stream);
 
 /*
+ * Forward for hosts that cannot give the library a workspace.  (No counterpart in the reference: its
+ * operators allocate their column buffer through PyTorch on every call.)
+ *
+ * Some embedders own device memory but no allocator they may call at this point: an engine plugin that is
+ * only handed input and output pointers, a runtime that carves one arena at start-up and forbids cudaMalloc
+ * afterwards because it synchronises the device and fragments the arena, a host that must not allocate
+ * between frames.  For them this entry point takes the same arguments as tvdcn_b200_deform_conv_forward
+ * minus the workspace and uses a scratch array compiled into the library instead:
+ * tvdcn_b200_static_scratch_bytes() bytes (16 MiB) of device memory that every GPU which loads the library
+ * holds until the process exits.  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ *  - A problem whose forward workspace (tvdcn_b200_forward_workspace_bytes) exceeds that size is refused with
+ *    TVDCN_ERR_WORKSPACE and a message that names both sizes; nothing is launched.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *    device current).  Make that first call outside any stream capture.
+ *  - All calls share the one array, and it keeps whatever the previous call left there.  The kernels
+ *    rewrite everything they read from it, so consecutive calls on one stream are independent; two calls that
+ *    overlap on the GPU (different streams, different threads) race on it and corrupt each other.
+ *  - Results are those of tvdcn_b200_deform_conv_forward for the same problem.
+ */
+int tvdcn_b200_deform_conv_forward_static(const tvdcn_problem *p,
+                                          const void *input, const void *weight,
+                                          const void *offset, const void *mask, const void *bias,
+                                          void *output, void *cuda_stream);
+size_t tvdcn_b200_static_scratch_bytes(void);
+
+/*
  * Backward.  Replaces deform_conv{1,2,3}d_backward_kernel
  *   (tvdcn/csrc/ops/cuda/deform_conv1d_kernel.cpp:343-559, deform_conv2d_kernel.cpp:387-642,
  *    deform_conv3d_kernel.cpp:431-725) and deform_conv_transpose{1,2,3}d_backward_kernel

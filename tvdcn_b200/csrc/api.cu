@@ -522,3 +522,56 @@ int tvdcn_b200_device_status(void) {
 uint64_t tvdcn_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"
+
+// ---- forward without a caller-provided workspace ---------------------------------------------------------
+// Scratch for tvdcn_b200_deform_conv_forward_static.  The array lives in this library's device image: every
+// GPU that loads the library keeps these bytes until the process exits.  In host code the name below is only
+// a handle for cudaGetSymbolAddress -- it is not a device address and must never be handed to a kernel.
+#define TVDCN_STATIC_SCRATCH_BYTES (16u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[TVDCN_STATIC_SCRATCH_BYTES];
+
+// Device address of the scratch array on the current device; looked up once per device.
+static cudaError_t static_scratch_address(void **out) {
+    static void *cached[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (cached[dev] == nullptr) {
+        void *addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_static_scratch);
+        if (e != cudaSuccess) return e;
+        cached[dev] = addr;
+    }
+    *out = cached[dev];
+    return cudaSuccess;
+}
+
+extern "C" {
+
+size_t tvdcn_b200_static_scratch_bytes(void) { return TVDCN_STATIC_SCRATCH_BYTES; }
+
+int tvdcn_b200_deform_conv_forward_static(const tvdcn_problem *p, const void *input, const void *weight,
+                                          const void *offset, const void *mask, const void *bias, void *output,
+                                          void *cuda_stream) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    rc = check_sizes(p);
+    if (rc) return rc;
+    const size_t need = plan_forward(p).total;
+    if (need > TVDCN_STATIC_SCRATCH_BYTES)
+        return fail(TVDCN_ERR_WORKSPACE,
+                    "this problem needs %zu bytes of scratch, more than the %u bytes built into the library; use "
+                    "tvdcn_b200_deform_conv_forward with a workspace of your own",
+                    need, (unsigned)TVDCN_STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    if (need > 0) {
+        const cudaError_t e = static_scratch_address(&scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+    }
+    // The forward kernels overwrite every scratch byte they later read (staged image, packed weights) and
+    // zero the scatter accumulator themselves, so nothing left by an earlier call can leak into this one.
+    return tvdcn_b200_deform_conv_forward(p, input, weight, offset, mask, bias, output, scratch, need, cuda_stream);
+}
+
+}  // extern "C"
