@@ -409,25 +409,42 @@ sample_wgrad_kernel(const Geo<DIM> g, const T *__restrict__ dense, const T *__re
     }
 }
 
-// out[c] = sum over batch and space of x[b, c, s]; one block per channel.
+// out[c] = sum over batch and space of x[b, c, s]; one 1024-thread block per channel: warp w walks the
+// images b = w, w + 32, ... and reads each contiguous row of S elements with 16-byte loads when it can.
 template <typename T, typename TO>
-__global__ void __launch_bounds__(256) channel_sum_kernel(const T *__restrict__ x, int B, int C, int S,
-                                                          TO *__restrict__ out) {
+__global__ void __launch_bounds__(1024) channel_sum_kernel(const T *__restrict__ x, int B, int C, int S,
+                                                           TO *__restrict__ out) {
     using A = acc_t<T>;
-    __shared__ A red[256];
+    constexpr int VEC = 16 / sizeof(T);
+    __shared__ A red[32];
     const int c = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool vec_ok = (S % VEC == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0);
     A sum = (A)0;
-    for (int b = 0; b < B; ++b) {
-        const int64_t base = ((int64_t)b * C + c) * (int64_t)S;
-        for (int s = threadIdx.x; s < S; s += blockDim.x) sum += load_acc(x, base + s);
+    for (int b = warp; b < B; b += 32) {
+        const T *row = x + ((int64_t)b * C + c) * (int64_t)S;
+        if (vec_ok) {
+            const uint4 *row16 = reinterpret_cast<const uint4 *>(row);
+            for (int i = lane; i < S / VEC; i += 32) {
+                const uint4 v = __ldg(row16 + i);
+                const T *e = reinterpret_cast<const T *>(&v);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) sum += to_acc(e[k]);
+            }
+        } else {
+            for (int s2 = lane; s2 < S; s2 += 32) sum += load_acc(row, s2);
+        }
     }
-    red[threadIdx.x] = sum;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) red[warp] = sum;
     __syncthreads();
-    for (int w = 128; w > 0; w >>= 1) {
-        if (threadIdx.x < w) red[threadIdx.x] += red[threadIdx.x + w];
-        __syncthreads();
+    if (warp == 0) {
+        A v = red[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) store_acc(out, c, v);
     }
-    if (threadIdx.x == 0) store_acc(out, c, red[0]);
 }
 
 template <typename A, typename T>
@@ -550,7 +567,7 @@ cudaError_t launch_channel_sum(int dtype, int out_dtype, const void *x, int B, i
         using T = std::remove_pointer_t<decltype(tp)>;
         using TO = std::remove_pointer_t<decltype(top)>;
         LaunchScope scope("channel_sum", stream);
-        channel_sum_kernel<T, TO><<<C, 256, 0, stream>>>((const T *)x, B, C, S, (TO *)out);
+        channel_sum_kernel<T, TO><<<C, 1024, 0, stream>>>((const T *)x, B, C, S, (TO *)out);
         return cudaGetLastError();
     });
 }

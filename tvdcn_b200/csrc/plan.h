@@ -74,6 +74,8 @@ cudaError_t launch_to_channels_last(const void *src, void *dst, int B, int C, in
 cudaError_t launch_pack_weight_ks(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
                                   void *lo, cudaStream_t stream);
 
+int tuning_int(const char *name, int fallback);
+
 // Address of the per-device status word the tensor-core kernels report failed bounded waits in.
 int *device_status_word();
 

@@ -48,16 +48,7 @@ __device__ __forceinline__ uint32_t sw128_offset(int row, int chunk) {
     return (uint32_t)row * 128u + (uint32_t)((chunk ^ (row & 7)) << 4);
 }
 
-// Per-position sampling plan of one (tap, offset group, mask group): for every corner of the 2^DIM cell
-// the row of the channels-last image it reads (batch * S + flat index; 0 when the corner is unused) and
-// its interpolation weight times the mask (0 when the corner is out of bounds).
-template <int DIM>
-struct PlanView {
-    int *rows;     // [1 << DIM][TILE_POS]
-    float *wts;    // [1 << DIM][TILE_POS]
-};
-
-// Decoded grid position of one thread, fixed for the life of a tile.
+// Decoded grid position of one thread.
 template <int DIM>
 struct PosInfo {
     bool valid;
@@ -66,11 +57,7 @@ struct PosInfo {
 };
 
 template <int DIM>
-__device__ __forceinline__ PosInfo<DIM> decode_position(const Geo<DIM> &g, long long idx) {
-    PosInfo<DIM> pi;
-    pi.valid = idx < g.BP;
-    pi.b = pi.valid ? (int)(idx / g.P) : 0;
-    pi.p = pi.valid ? (int)(idx % g.P) : 0;
+__device__ __forceinline__ void decode_in_image(const Geo<DIM> &g, PosInfo<DIM> &pi) {
     int r = pi.p;
 #pragma unroll
     for (int a = DIM - 1; a >= 0; --a) {
@@ -78,14 +65,69 @@ __device__ __forceinline__ PosInfo<DIM> decode_position(const Geo<DIM> &g, long 
         r /= g.grid[a];
         pi.base[a] = c * g.stride[a] - g.pad[a];
     }
+}
+
+template <int DIM>
+__device__ __forceinline__ PosInfo<DIM> decode_position(const Geo<DIM> &g, long long idx) {
+    PosInfo<DIM> pi;
+    pi.valid = idx < g.BP;
+    pi.b = pi.valid ? (int)(idx / g.P) : 0;
+    pi.p = pi.valid ? (int)(idx % g.P) : 0;
+    decode_in_image<DIM>(g, pi);
     return pi;
 }
 
-// Fills this thread's slot of the plan.  want_deriv == false: weights are interpolation weight * mask.
+// ---- sampling plan ------------------------------------------------------------------------------------
+// One entry per (position, corner of the 2^DIM cell): where the corner's 64-channel row starts in the
+// channels-last image, in 16-byte units, and the corner's interpolation weight times the mask -- as a packed
+// 16-bit pair (w, w) for 16-bit data, as f32 bits for f32 data.  Unused / out-of-bounds corners point at row 0
+// with weight 0, so the producers can load unconditionally.
+struct PlanEntry {
+    uint32_t row16;
+    uint32_t w;
+};
+
+// Offsets and mask of one (position, tap, groups): loaded early, turned into plan entries later, so that the
+// global-memory latency overlaps the sampling of the previous chunk.
 template <int DIM>
-__device__ __forceinline__ void fill_plan(const Geo<DIM> &g, const PosInfo<DIM> &pi, const float *__restrict__ offset,
-                                          const float *__restrict__ mask, int tap, int ogi, int mgi, int slot, int pstride,
-                                          PlanView<DIM> pv) {
+struct RawCoords {
+    float off[DIM];
+    float m;
+};
+
+template <int DIM>
+__device__ __forceinline__ RawCoords<DIM> load_coords(const Geo<DIM> &g, const PosInfo<DIM> &pi,
+                                                      const float *__restrict__ offset,
+                                                      const float *__restrict__ mask, int tap, int ogi, int mgi) {
+    RawCoords<DIM> rc;
+#pragma unroll
+    for (int a = 0; a < DIM; ++a)
+        rc.off[a] = (offset != nullptr && pi.valid)
+                        ? __ldg(offset + ((((int64_t)pi.b * g.og + ogi) * g.K + tap) * DIM + a) * (int64_t)g.P + pi.p)
+                        : 0.f;
+    rc.m = (mask != nullptr && pi.valid)
+               ? __ldg(mask + (((int64_t)pi.b * g.mg + mgi) * g.K + tap) * (int64_t)g.P + pi.p)
+               : 1.f;
+    return rc;
+}
+
+template <int MODE>
+__device__ __forceinline__ uint32_t encode_weight(float w) {
+    if constexpr (MODE == TC_SPLIT) {
+        return __float_as_uint(w);
+    } else if constexpr (MODE == TC_F16) {
+        const __half2 h = __float2half2_rn(w);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    } else {
+        const __nv_bfloat162 h = __float2bfloat162_rn(w);
+        return *reinterpret_cast<const uint32_t *>(&h);
+    }
+}
+
+// Writes the NC plan entries of one position.  row_scale = Cs * element size / 16.
+template <int DIM, int MODE>
+__device__ __forceinline__ void build_plan(const Geo<DIM> &g, const PosInfo<DIM> &pi, const RawCoords<DIM> &rc,
+                                           bool deformable, int tap, uint32_t row_scale, PlanEntry *slot) {
     constexpr int NC = 1 << DIM;
     int fl[DIM];
     float fr[DIM];
@@ -99,9 +141,8 @@ __device__ __forceinline__ void fill_plan(const Geo<DIM> &g, const PosInfo<DIM> 
 #pragma unroll
     for (int a = 0; a < DIM; ++a) {
         const int base = pi.base[a] + tc[a] * g.dil[a];
-        if (offset != nullptr && pi.valid) {
-            const float o = __ldg(offset + ((((int64_t)pi.b * g.og + ogi) * g.K + tap) * DIM + a) * (int64_t)g.P + pi.p);
-            const float pos = (float)base + o;
+        if (deformable) {
+            const float pos = (float)base + rc.off[a];
             const float f = floorf(pos);
             fl[a] = (int)f;
             fr[a] = pos - f;
@@ -110,13 +151,11 @@ __device__ __forceinline__ void fill_plan(const Geo<DIM> &g, const PosInfo<DIM> 
             fr[a] = 0.f;
         }
     }
-    float m = 1.f;
-    if (mask != nullptr && pi.valid) m = __ldg(mask + (((int64_t)pi.b * g.mg + mgi) * g.K + tap) * (int64_t)g.P + pi.p);
 #pragma unroll
     for (int c = 0; c < NC; ++c) {
-        bool ok = pi.valid && (offset != nullptr || c == 0);
+        bool ok = pi.valid && (deformable || c == 0);
         int flat = 0;
-        float w = m;
+        float w = rc.m;
 #pragma unroll
         for (int a = 0; a < DIM; ++a) {
             const int bit = (c >> (DIM - 1 - a)) & 1;
@@ -125,8 +164,10 @@ __device__ __forceinline__ void fill_plan(const Geo<DIM> &g, const PosInfo<DIM> 
             flat = flat * g.img[a] + i;
             w *= bit ? fr[a] : (1.f - fr[a]);
         }
-        pv.rows[c * pstride + slot] = ok ? pi.b * g.S + flat : 0;
-        pv.wts[c * pstride + slot] = ok ? w : 0.f;
+        PlanEntry e;
+        e.row16 = ok ? (uint32_t)(pi.b * g.S + flat) * row_scale : 0u;
+        e.w = encode_weight<MODE>(ok ? w : 0.f);
+        slot[c] = e;
     }
 }
 
@@ -156,104 +197,110 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, __half) {
     return *reinterpret_cast<const uint32_t *>(&h);
 }
 
-// Samples `npos` positions x 64 channels into a 128-byte-swizzled tile (row = position).  `rows` / `wts`
-// are one plan ([NC][TILE_POS], entry = position within the tile).  All NT threads take part; loads are
-// issued unconditionally (unused corners point at row 0 with weight 0) and in batches of up to 16 per
-// thread so that global-memory latency is overlapped instead of being paid once per corner.
-//   MODE TC_BF16 / TC_F16: img_cl is 16-bit, one tile `hi`.
-//   MODE TC_SPLIT: img_cl is f32, the blended value is split into bf16 hi + lo tiles.
-template <int NC, int MODE, int NT>
-__device__ __forceinline__ void produce_tile(uint8_t *hi, uint8_t *lo, const void *img_cl, int Cs, int chan0,
-                                             const int *rows, const float *wts, int pstride, int npos, int tid) {
-    constexpr int IB = NC >= 8 ? 2 : 4;  // positions per thread whose loads are in flight together
-    if constexpr (MODE != TC_SPLIT) {
-        using T16 = typename std::conditional<MODE == TC_F16, __half, __nv_bfloat16>::type;
-        const T16 *img = reinterpret_cast<const T16 *>(img_cl) + chan0 + (tid & 7) * 8;
-        constexpr int PPI = NT / 8;  // positions covered by one pass of all threads (8 lanes per position)
-        const int psub = tid >> 3;
-        for (int p0 = 0; p0 < npos; p0 += PPI * IB) {
-            uint4 v[IB][NC];
-            float w[IB][NC];
+// acc (+)= w * v on packed 16-bit pairs (the blend of 16-bit data stays in its own precision: the result is
+// rounded to that precision for the tensor core anyway)
+template <typename T16>
+__device__ __forceinline__ uint32_t fma2(uint32_t w, uint32_t v, uint32_t acc) {
+    if constexpr (std::is_same<T16, __half>::value) {
+        const __half2 r = __hfma2(*reinterpret_cast<const __half2 *>(&w), *reinterpret_cast<const __half2 *>(&v),
+                                  *reinterpret_cast<const __half2 *>(&acc));
+        return *reinterpret_cast<const uint32_t *>(&r);
+    } else {
+        const __nv_bfloat162 r = __hfma2(*reinterpret_cast<const __nv_bfloat162 *>(&w),
+                                         *reinterpret_cast<const __nv_bfloat162 *>(&v),
+                                         *reinterpret_cast<const __nv_bfloat162 *>(&acc));
+        return *reinterpret_cast<const uint32_t *>(&r);
+    }
+}
+template <typename T16>
+__device__ __forceinline__ uint32_t mul2(uint32_t w, uint32_t v) {
+    if constexpr (std::is_same<T16, __half>::value) {
+        const __half2 r = __hmul2(*reinterpret_cast<const __half2 *>(&w), *reinterpret_cast<const __half2 *>(&v));
+        return *reinterpret_cast<const uint32_t *>(&r);
+    } else {
+        const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&w),
+                                         *reinterpret_cast<const __nv_bfloat162 *>(&v));
+        return *reinterpret_cast<const uint32_t *>(&r);
+    }
+}
+
+// Samples `nvpos` virtual positions x 64 channels into 128-byte-swizzled tiles (row = position).  Virtual
+// position v belongs to sub-tile v / pos_per_sub (tiles `sub_bytes` apart, each with its own first channel
+// chan16[sub], in 16-byte units) and is row v % pos_per_sub of it.  plan[v * NC + c] is the entry of corner c.
+// All NT threads take part; each keeps the loads of IB positions in flight together so that global-memory
+// latency is overlapped.  nvpos must be a multiple of (NT / lanes-per-position) * IB.
+//   MODE TC_BF16 / TC_F16: img16 is the 16-bit image, one tile `hi`; 8 lanes x 8 channels per position.
+//   MODE TC_SPLIT: img16 is the f32 image, the blend is split into bf16 hi + lo; 16 lanes x 4 channels.
+template <int NC, int MODE, int NT, int IB = (NC >= 8 ? 2 : 4)>
+__device__ __forceinline__ void produce_tiles(uint8_t *hi, uint8_t *lo, uint32_t sub_bytes, int pos_per_sub, int nvpos,
+                                              const uint4 *__restrict__ img16, const uint32_t *chan16,
+                                              const PlanEntry *plan, int tid) {
+    constexpr int LPP = MODE == TC_SPLIT ? 16 : 8;
+    constexpr int PPI = NT / LPP;
+    const int part = tid & (LPP - 1);
+    const int psub = tid / LPP;
+    for (int v0 = 0; v0 < nvpos; v0 += PPI * IB) {
+        uint4 v[IB][NC];
+        uint32_t w[IB][NC];
 #pragma unroll
-            for (int i = 0; i < IB; ++i) {
-                const int pos = p0 + i * PPI + psub;
-                if (pos < npos) {
+        for (int i = 0; i < IB; ++i) {
+            const int vp = v0 + i * PPI + psub;
+            const uint4 *src = img16 + chan16[(v0 + i * PPI) / pos_per_sub] + part;
+            const PlanEntry *pe = plan + vp * NC;
 #pragma unroll
-                    for (int c = 0; c < NC; ++c) {
-                        w[i][c] = wts[c * pstride + pos];
-                        v[i][c] = __ldg(reinterpret_cast<const uint4 *>(img + (int64_t)rows[c * pstride + pos] * Cs));
-                    }
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < IB; ++i) {
-                const int pos = p0 + i * PPI + psub;
-                if (pos < npos) {
-                    float acc[8];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-#pragma unroll
-                    for (int c = 0; c < NC; ++c) {
-                        float f[8];
-                        unpack8(v[i][c], f, T16());
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[i][c], f[e], acc[e]);
-                    }
-                    uint4 o;
-                    o.x = pack2(acc[0], acc[1], T16());
-                    o.y = pack2(acc[2], acc[3], T16());
-                    o.z = pack2(acc[4], acc[5], T16());
-                    o.w = pack2(acc[6], acc[7], T16());
-                    *reinterpret_cast<uint4 *>(hi + sw128_offset(pos, tid & 7)) = o;
-                }
+            for (int c = 0; c < NC; ++c) {
+                const PlanEntry e = pe[c];
+                w[i][c] = e.w;
+                v[i][c] = __ldg(src + e.row16);
             }
         }
-    } else {
-        const int quad = tid & 15;
-        const float *img = reinterpret_cast<const float *>(img_cl) + chan0 + quad * 4;
-        constexpr int PPI = NT / 16;  // 16 lanes (4 channels each) per position
-        const int psub = tid >> 4;
-        for (int p0 = 0; p0 < npos; p0 += PPI * IB) {
-            float4 v[IB][NC];
-            float w[IB][NC];
 #pragma unroll
-            for (int i = 0; i < IB; ++i) {
-                const int pos = p0 + i * PPI + psub;
-                if (pos < npos) {
+        for (int i = 0; i < IB; ++i) {
+            const int vp = v0 + i * PPI + psub;
+            const int sub = (v0 + i * PPI) / pos_per_sub;
+            const int pos = vp - sub * pos_per_sub;
+            uint8_t *dst_hi = hi + (size_t)sub * sub_bytes;
+            if constexpr (MODE != TC_SPLIT) {
+                using T16 = typename std::conditional<MODE == TC_F16, __half, __nv_bfloat16>::type;
+                uint4 o;
+                o.x = mul2<T16>(w[i][0], v[i][0].x);
+                o.y = mul2<T16>(w[i][0], v[i][0].y);
+                o.z = mul2<T16>(w[i][0], v[i][0].z);
+                o.w = mul2<T16>(w[i][0], v[i][0].w);
 #pragma unroll
-                    for (int c = 0; c < NC; ++c) {
-                        w[i][c] = wts[c * pstride + pos];
-                        v[i][c] = __ldg(reinterpret_cast<const float4 *>(img + (int64_t)rows[c * pstride + pos] * Cs));
-                    }
+                for (int c = 1; c < NC; ++c) {
+                    o.x = fma2<T16>(w[i][c], v[i][c].x, o.x);
+                    o.y = fma2<T16>(w[i][c], v[i][c].y, o.y);
+                    o.z = fma2<T16>(w[i][c], v[i][c].z, o.z);
+                    o.w = fma2<T16>(w[i][c], v[i][c].w, o.w);
                 }
-            }
+                *reinterpret_cast<uint4 *>(dst_hi + sw128_offset(pos, part)) = o;
+            } else {
+                uint8_t *dst_lo = lo + (size_t)sub * sub_bytes;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < IB; ++i) {
-                const int pos = p0 + i * PPI + psub;
-                if (pos < npos) {
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int c = 0; c < NC; ++c) {
-                        acc[0] = fmaf(w[i][c], v[i][c].x, acc[0]);
-                        acc[1] = fmaf(w[i][c], v[i][c].y, acc[1]);
-                        acc[2] = fmaf(w[i][c], v[i][c].z, acc[2]);
-                        acc[3] = fmaf(w[i][c], v[i][c].w, acc[3]);
-                    }
-                    float h[4], l[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        h[e] = __bfloat162float(__float2bfloat16_rn(acc[e]));
-                        l[e] = acc[e] - h[e];
-                    }
-                    uint2 oh, ol;
-                    oh.x = pack2(h[0], h[1], __nv_bfloat16());
-                    oh.y = pack2(h[2], h[3], __nv_bfloat16());
-                    ol.x = pack2(l[0], l[1], __nv_bfloat16());
-                    ol.y = pack2(l[2], l[3], __nv_bfloat16());
-                    const uint32_t off = sw128_offset(pos, quad >> 1) + (uint32_t)(quad & 1) * 8u;
-                    *reinterpret_cast<uint2 *>(hi + off) = oh;
-                    *reinterpret_cast<uint2 *>(lo + off) = ol;
+                for (int c = 0; c < NC; ++c) {
+                    const float wf = __uint_as_float(w[i][c]);
+                    acc[0] = fmaf(wf, __uint_as_float(v[i][c].x), acc[0]);
+                    acc[1] = fmaf(wf, __uint_as_float(v[i][c].y), acc[1]);
+                    acc[2] = fmaf(wf, __uint_as_float(v[i][c].z), acc[2]);
+                    acc[3] = fmaf(wf, __uint_as_float(v[i][c].w), acc[3]);
                 }
+                // hi = bf16(acc) by truncation-free rounding, lo = bf16(acc - hi)
+                const uint32_t h01 = pack2(acc[0], acc[1], __nv_bfloat16());
+                const uint32_t h23 = pack2(acc[2], acc[3], __nv_bfloat16());
+                const float l0 = acc[0] - __uint_as_float(h01 << 16);
+                const float l1 = acc[1] - __uint_as_float(h01 & 0xffff0000u);
+                const float l2 = acc[2] - __uint_as_float(h23 << 16);
+                const float l3 = acc[3] - __uint_as_float(h23 & 0xffff0000u);
+                uint2 oh, ol;
+                oh.x = h01;
+                oh.y = h23;
+                ol.x = pack2(l0, l1, __nv_bfloat16());
+                ol.y = pack2(l2, l3, __nv_bfloat16());
+                const uint32_t off = sw128_offset(pos, part >> 1) + (uint32_t)(part & 1) * 8u;
+                *reinterpret_cast<uint2 *>(dst_hi + off) = oh;
+                *reinterpret_cast<uint2 *>(dst_lo + off) = ol;
             }
         }
     }
@@ -264,19 +311,5 @@ __device__ __forceinline__ void produce_tile(uint8_t *hi, uint8_t *lo, const voi
 // entry point is unavailable or rejects the description.
 bool make_tensor_map_16bit(CUtensorMap *map, const void *base, int rank, const uint64_t *dims,
                            const uint64_t *strides_bytes /* rank-1 entries */, const uint32_t *box);
-
-// [B, C, S] -> [B, S, C], element size 2 or 4 bytes.
-cudaError_t launch_to_channels_last(const void *src, void *dst, int B, int C, int S, int elem_bytes,
-                                    cudaStream_t stream);
-// [B, S, C] f32 -> [B, C, S] f32 (grad buffers coming back from channels-last accumulation).
-cudaError_t launch_from_channels_last_f32(const float *src, void *dst, int dst_dtype, int B, int C, int S,
-                                          cudaStream_t stream);
-
-// weight [Cd, csg, K] (dtype: f32 / bf16 / f16) -> packed[g][tap][d'][s'] 16-bit (hi) and, in split mode, lo.
-cudaError_t launch_pack_weight_ks(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
-                                  void *lo, cudaStream_t stream);
-// same source -> packed[g][tap][s'][d'] (reduction over dense channels contiguous)
-cudaError_t launch_pack_weight_kd(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
-                                  void *lo, cudaStream_t stream);
 
 }  // namespace tvdcn_b200

@@ -51,6 +51,12 @@ constexpr int DG_THREADS = DG_EPI_WARPS * 32 + 64;
 constexpr int DG_A_TILE = 128 * 128;   // [128 pos][64 d] 16-bit
 constexpr int DG_TMEM_COLS = 512;
 
+// where one corner of one position scatters to (row of the channels-last image) and with what factor
+struct ScatterInfo {
+    int row;
+    float scale;
+};
+
 __device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                  : "memory");
@@ -130,6 +136,10 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
     uint64_t *t_full = b_empty + BS;
     uint64_t *t_empty = t_full + 8;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(t_empty + 8);
+    // per-epilogue-warp staging for the transposed scatter: [32 pos][32 ch] f32 + [32 pos][NC] corner info
+    float *stage_g = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));
+    ScatterInfo *stage_c = reinterpret_cast<ScatterInfo *>(stage_g + DG_EPI_WARPS * 32 * 32);
+    float *stage_d = reinterpret_cast<float *>(stage_c + DG_EPI_WARPS * 32 * NC);   // [warp][32 pos][NC] dot products
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int grp = blockIdx.y;
@@ -200,8 +210,8 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
         bool ok = true;
         for (int blk = 0; blk < n_blocks; ++blk) {
             const int q = blk % NQ;
-            const int tap = blk / blocks_per_tap;
-            const int cc0 = (blk % blocks_per_tap) * NB;
+            const int tap = blk % g.K;
+            const int cc0 = (blk / g.K) * NB;
             if (ok && !ptx::mbar_wait(&t_full[q], (uint32_t)((blk / NQ) & 1))) {
                 atomicExch(P.status, 301);
                 ok = false;
@@ -249,6 +259,7 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                 }
                 // corner geometry of this (position, tap, offset group)
                 int64_t row[NC];
+                int rowi[NC];
                 float wc[NC];
                 bool okc[NC];
 #pragma unroll
@@ -266,62 +277,110 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                     }
                     okc[c] = v;
                     wc[c] = v ? w : 0.f;
-                    row[c] = v ? ((int64_t)pi.b * g.S + flat) * g.Cs : 0;
+                    rowi[c] = v ? pi.b * g.S + flat : 0;
+                    row[c] = (int64_t)rowi[c] * g.Cs;
                 }
                 // this warp's 32 columns of the chunk
                 uint32_t raw[32];
                 ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(lane_q * 32) << 16) + (uint32_t)(q * ncol + ci * 64 + half * 32),
                                    raw);
                 ptx::tmem_ld_wait();
-                if (pi.valid) {
-                    float gv[32];
+                // Transpose through shared memory: afterwards a few lanes share one position and cover a
+                // contiguous piece of an image row, so a warp-wide load or vector reduction touches 4-8 rows
+                // instead of 32 (thread = position would make every access a 32-row gather).
+                float *gs = stage_g + warp * 32 * 32;
+                ScatterInfo *cs = stage_c + warp * 32 * NC;
+                float *ds_ = stage_d + warp * 32 * NC;
+                const int ch0 = chan0 + half * 32;
+                __syncwarp();
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) gv[e] = __uint_as_float(raw[e]);
-                    const int ch0 = chan0 + half * 32;
-                    if (want_coord) {
-                        float dotc[NC];
+                for (int i = 0; i < 8; ++i) {
+                    float4 qv;
+                    qv.x = __uint_as_float(raw[4 * i]);
+                    qv.y = __uint_as_float(raw[4 * i + 1]);
+                    qv.z = __uint_as_float(raw[4 * i + 2]);
+                    qv.w = __uint_as_float(raw[4 * i + 3]);
+                    *reinterpret_cast<float4 *>(gs + lane * 32 + ((i ^ (lane & 7)) << 2)) = qv;
+                }
 #pragma unroll
-                        for (int c = 0; c < NC; ++c) dotc[c] = 0.f;
+                for (int c = 0; c < NC; ++c) {
+                    ScatterInfo si;
+                    si.row = rowi[c];
+                    si.scale = okc[c] ? mval * wc[c] : 0.f;
+                    cs[lane * NC + c] = si;
+                }
+                __syncwarp();
+                if (want_coord) {
+                    // 4 lanes per position, 8 channels each: dot products <col, corner row> reduced over the 4 lanes
+                    const int q4 = lane & 3, p8 = lane >> 2;
+                    // loads of ITB iterations (8 positions each) are issued together so that their latency overlaps
+                    constexpr int ITB = SPLIT ? 2 : 4;
 #pragma unroll
-                        for (int piece = 0; piece < 32 / PS; ++piece) {
-                            CornerLoad<PS, TI> cl[NC];
+                    for (int it0 = 0; it0 < 4; it0 += ITB) {
+                        CornerLoad<8, TI> cl[ITB][NC];
 #pragma unroll
-                            for (int c = 0; c < NC; ++c) cl[c].load(img + row[c] + ch0 + piece * PS);
+                        for (int i = 0; i < ITB; ++i) {
+                            const int pos = (it0 + i) * 8 + p8;
 #pragma unroll
-                            for (int c = 0; c < NC; ++c) dotc[c] += cl[c].dot(gv + piece * PS);
+                            for (int c = 0; c < NC; ++c)
+                                cl[i][c].load(img + (int64_t)cs[pos * NC + c].row * g.Cs + ch0 + q4 * 8);
                         }
-                        float s_val = 0.f;
 #pragma unroll
-                        for (int c = 0; c < NC; ++c) s_val = fmaf(wc[c], dotc[c], s_val);
-                        gm_sum += s_val;
-                        if (P.goff != nullptr) {
+                        for (int i = 0; i < ITB; ++i) {
+                            const int pos = (it0 + i) * 8 + p8;
+                            const float4 g0 = *reinterpret_cast<const float4 *>(gs + pos * 32 + (((2 * q4) ^ (pos & 7)) << 2));
+                            const float4 g1 = *reinterpret_cast<const float4 *>(gs + pos * 32 + (((2 * q4 + 1) ^ (pos & 7)) << 2));
+                            const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
 #pragma unroll
-                            for (int a = 0; a < DIM; ++a) {
-                                float ds = 0.f;
-#pragma unroll
-                                for (int c = 0; c < NC; ++c) {
-                                    if (okc[c]) {
-                                        float w = ((c >> (DIM - 1 - a)) & 1) ? 1.f : -1.f;
-#pragma unroll
-                                        for (int a2 = 0; a2 < DIM; ++a2)
-                                            if (a2 != a) w *= ((c >> (DIM - 1 - a2)) & 1) ? fr[a2] : (1.f - fr[a2]);
-                                        ds = fmaf(w, dotc[c], ds);
-                                    }
-                                }
-                                go_sum[a] = fmaf(mval, ds, go_sum[a]);
+                            for (int c = 0; c < NC; ++c) {
+                                float d = cl[i][c].dot(gg);
+                                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                                if (q4 == 0) ds_[pos * NC + c] = d;
                             }
                         }
                     }
-                    if (P.img_grad_cl != nullptr) {
+                }
+                if (P.img_grad_cl != nullptr) {
+                    const int quad = lane & 7;
+                    float *dst0 = P.img_grad_cl + ch0 + quad * 4;
+#pragma unroll 2
+                    for (int it = 0; it < 8; ++it) {
+                        const int pos = it * 4 + (lane >> 3);
+                        const float4 qv = *reinterpret_cast<const float4 *>(gs + pos * 32 + ((quad ^ (pos & 7)) << 2));
 #pragma unroll
                         for (int c = 0; c < NC; ++c) {
-                            if (okc[c]) {
-                                const float sc = mval * wc[c];
-                                float *dst = P.img_grad_cl + row[c] + ch0;
+                            const ScatterInfo si = cs[pos * NC + c];
+                            if (si.scale != 0.f)
+                                red_add_v4(dst0 + (int64_t)si.row * g.Cs, qv.x * si.scale, qv.y * si.scale, qv.z * si.scale,
+                                           qv.w * si.scale);
+                        }
+                    }
+                }
+                if (want_coord) {
+                    __syncwarp();
+                    float dotc[NC];
 #pragma unroll
-                                for (int e = 0; e < 32; e += 4)
-                                    red_add_v4(dst + e, gv[e] * sc, gv[e + 1] * sc, gv[e + 2] * sc, gv[e + 3] * sc);
+                    for (int c = 0; c < NC; ++c) dotc[c] = ds_[lane * NC + c];
+                    float s_val = 0.f;
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) s_val = fmaf(wc[c], dotc[c], s_val);
+                    gm_sum += s_val;
+                    if (P.goff != nullptr) {
+#pragma unroll
+                        for (int a = 0; a < DIM; ++a) {
+                            float ds = 0.f;
+#pragma unroll
+                            for (int c = 0; c < NC; ++c) {
+                                if (okc[c]) {
+                                    float w = ((c >> (DIM - 1 - a)) & 1) ? 1.f : -1.f;
+#pragma unroll
+                                    for (int a2 = 0; a2 < DIM; ++a2)
+                                        if (a2 != a) w *= ((c >> (DIM - 1 - a2)) & 1) ? fr[a2] : (1.f - fr[a2]);
+                                    ds = fmaf(w, dotc[c], ds);
+                                }
                             }
+                            go_sum[a] = fmaf(mval, ds, go_sum[a]);
                         }
                     }
                 }
@@ -391,8 +450,8 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
             int j = 0, issued = 0;
             bool ok = true;
             for (int blk = 0; blk < n_blocks && ok; ++blk) {
-                const int tap = blk / blocks_per_tap;
-                const int cc0 = (blk % blocks_per_tap) * NB;
+                const int tap = blk % g.K;
+                const int cc0 = (blk / g.K) * NB;
                 for (int rc = 0; rc < RC; ++rc, ++j) {
                     const int s = j % BS;
                     if (!ptx::mbar_wait(&b_empty[s], (uint32_t)(((j / BS) & 1) ^ 1))) {
@@ -479,8 +538,9 @@ __global__ void __launch_bounds__(256) from_channels_last_bias_kernel(const floa
 
 size_t dgrad_smem_bytes(int mode, int rc, int nb, int b_stages) {
     const int parts = mode == TC_SPLIT ? 2 : 1;
+    const size_t staging = (size_t)DG_EPI_WARPS * (32 * 32 * 4 + 32 * 8 * 8 + 32 * 8 * 4);  // epilogue transposition buffers
     return 1024 + (size_t)rc * parts * DG_A_TILE + (size_t)b_stages * parts * nb * 64 * 128 + (1 + 2 * b_stages + 16) * 8 +
-           16;
+           48 + staging;
 }
 
 template <int DIM, int MODE>
@@ -498,11 +558,13 @@ cudaError_t launch_dgrad_t(const DgradParams<DIM> &P, dim3 grid, const CUtensorM
 
 bool dgrad_tc_config(int mode, int cdg, int csg, int *nb, int *b_stages) {
     const int rc = cdg / 64;
-    const int n = ((csg / 64) % 2 == 0) ? 2 : 1;
+    int n = ((csg / 64) % 2 == 0) ? 2 : 1;
     int s = 0;
-    for (int cand = 6; cand >= 2; --cand)
-        if (dgrad_smem_bytes(mode, rc, n, cand) <= 227 * 1024) { s = cand; break; }
+    for (; n >= 1 && s == 0; --n)
+        for (int cand = tuning_int("TVDCN_B200_DG_STAGES", 4); cand >= 2; --cand)
+            if (dgrad_smem_bytes(mode, rc, n, cand) <= 227 * 1024) { s = cand; break; }
     if (s == 0) return false;
+    ++n;  // undo the loop's last decrement
     *nb = n;
     *b_stages = s;
     return true;

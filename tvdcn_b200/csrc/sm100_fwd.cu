@@ -11,8 +11,11 @@
 // (tcgen05.ld: lane = position) and store NCHW with the bias added, so the reference's output_buf
 // transpose and bias pass (tvdcn/csrc/ops/cuda/deform_conv2d_kernel.cpp:371-380) are gone too.
 //
-// Warp roles (320 threads): warps 0-7 producers + epilogue, warp 8 MMA issue + TMEM owner, warp 9 TMA.
+// Warp roles (704 threads): warps 0-15 producers + epilogue, warp 16 MMA issue + TMEM owner, warp 17 TMA,
+// warps 18-21 planners (sampling coordinates -> plan entries + L1 prefetch, a few chunks ahead).
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <type_traits>
 
 #include "plan.h"
@@ -32,13 +35,20 @@ struct FwdParams {
     int bn;                 // dense channels per tile: 64, 128 or 256
     int stages;
     int chunks_per_tap;     // csg / 64
+    int prefetch;           // planners also issue L1 prefetches of the corner rows
+    long long *prof;        // optional cycle counters of CTA 0 (tuning aid), else null
 };
 
 namespace {
 
-constexpr int PRODUCER_WARPS = 8;
+constexpr int PRODUCER_WARPS = 16;
 constexpr int PRODUCERS = PRODUCER_WARPS * 32;
-constexpr int FWD_THREADS = PRODUCERS + 64;
+constexpr int PGROUPS = 2;                        // producer groups; group q samples chunks j with j % PGROUPS == q
+constexpr int GROUP_WARPS = PRODUCER_WARPS / PGROUPS;
+constexpr int GROUP_THREADS = GROUP_WARPS * 32;
+constexpr int PLANNER_WARPS = 4;                  // one planner thread per tile position
+constexpr int PLAN_BUFS = 4;
+constexpr int FWD_THREADS = PRODUCERS + 64 + PLANNER_WARPS * 32;
 
 template <int DIM, int MODE>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
@@ -59,14 +69,15 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
     const uint32_t b_stage_bytes = b_part_bytes * PARTS;
     uint8_t *sA = smem;
     uint8_t *sB = sA + (size_t)S * a_stage_bytes;
-    int *plan_rows = reinterpret_cast<int *>(sB + (size_t)S * b_stage_bytes);  // [2][NC][128]
-    float *plan_wts = reinterpret_cast<float *>(plan_rows + 2 * NC * TILE_POS);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(plan_wts + 2 * NC * TILE_POS);
+    PlanEntry *plan = reinterpret_cast<PlanEntry *>(sB + (size_t)S * b_stage_bytes);  // [PLAN_BUFS][128][NC]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(plan + PLAN_BUFS * NC * TILE_POS);
     uint64_t *full_a = bars;
     uint64_t *full_b = bars + S;
     uint64_t *empty = bars + 2 * S;
     uint64_t *accum = bars + 3 * S;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+    uint64_t *plan_full = bars + 3 * S + 1;
+    uint64_t *plan_empty = plan_full + PLAN_BUFS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(plan_empty + PLAN_BUFS);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = g.cdg / BN;
@@ -78,11 +89,15 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            ptx::mbar_init(&full_a[s], PRODUCER_WARPS);
+            ptx::mbar_init(&full_a[s], GROUP_WARPS);
             ptx::mbar_init(&full_b[s], 1);
             ptx::mbar_init(&empty[s], 1);
         }
         ptx::mbar_init(accum, 1);
+        for (int b = 0; b < PLAN_BUFS; ++b) {
+            ptx::mbar_init(&plan_full[b], PLANNER_WARPS);
+            ptx::mbar_init(&plan_empty[b], GROUP_WARPS);
+        }
         ptx::fence_mbar_init();
     }
     if (warp == PRODUCER_WARPS + 1 && lane == 0) {
@@ -98,44 +113,59 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    constexpr uint32_t ESZ = SPLIT ? 4 : 2;
+    const uint4 *img16 = reinterpret_cast<const uint4 *>(P.img_cl);
+    // chunk j -> (tap, first channel): channel chunk outermost, so the taps of one 64-channel chunk sample the
+    // same slab of the image, which then stays in L1 for all of them
+    auto chunk_tap = [&](int j) { return j % g.K; };
+    auto chunk_chan0 = [&](int j) { return grp * g.csg + (j / g.K) * CHUNK_C; };
+
     if (warp < PRODUCER_WARPS) {
         // ------------------------------------------------------------------ producers
         const int t = threadIdx.x;
-        // position this thread plans for (threads 0..127) and stores in the epilogue (TMEM lane of its warp)
-        const int my_pos = (warp & 3) * 32 + lane;
-        const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + my_pos);
-        int cur_tap = -1, cur_og = -1, cur_mg = -1, pb = 1;
+        // position this thread stores in the epilogue (TMEM lane of its warp)
+        const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + (warp & 3) * 32 + lane);
+        const bool prof_on = P.prof != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && t == 0;
+        long long t_wait = 0, t_prod = 0, t_sig = 0, t_plan = 0, t0 = 0, t_begin = 0;
+        if (prof_on) t_begin = clock64();
         bool ok = true;
-        // A failed wait never leaves the loop early: every producer keeps taking part in the named barrier
-        // below, it only stops touching shared memory and stops signalling.
-        for (int j = 0; j < n_chunks; ++j) {
+        // Two groups of producer warps take alternate chunks, so that one group's loads are in flight while the
+        // other blends and stores: the load/store pipe stays busy instead of idling between phases.
+        const int pgroup = warp / GROUP_WARPS;
+        const int tg = t % GROUP_THREADS;
+        for (int j = pgroup; j < n_chunks; j += PGROUPS) {
             const int s = j % S, r = j / S;
-            const int tap = j / P.chunks_per_tap, cc = j % P.chunks_per_tap;
-            const int chan0 = grp * g.csg + cc * CHUNK_C;
-            const int ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
-            const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
-            if (tap != cur_tap || ogi != cur_og || mgi != cur_mg) {
-                pb ^= 1;
-                if (t < TILE_POS) {
-                    PlanView<DIM> pv{plan_rows + pb * NC * TILE_POS, plan_wts + pb * NC * TILE_POS};
-                    fill_plan<DIM>(g, pi, P.offset, P.mask, tap, ogi, mgi, t, TILE_POS, pv);
-                }
-                cur_tap = tap; cur_og = ogi; cur_mg = mgi;
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+            const int pbuf = j % PLAN_BUFS;
+            if (prof_on) t0 = clock64();
+            if (ok && !ptx::mbar_wait(&plan_full[pbuf], (uint32_t)((j / PLAN_BUFS) & 1))) {
+                atomicExch(P.status, 105);
+                ok = false;
             }
-            const int *rows = plan_rows + pb * NC * TILE_POS;
-            const float *wts = plan_wts + pb * NC * TILE_POS;
+            if (prof_on) { const long long t1 = clock64(); t_plan += t1 - t0; t0 = t1; }
             if (ok && !ptx::mbar_wait(&empty[s], (uint32_t)((r & 1) ^ 1))) {
                 atomicExch(P.status, 101);
                 ok = false;
             }
             ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the __syncwarp below
-            if (!ok) continue;
+            if (prof_on) { const long long t1 = clock64(); t_wait += t1 - t0; t0 = t1; }
+            if (!ok) break;
             uint8_t *a_hi = sA + (size_t)s * a_stage_bytes;
-            produce_tile<NC, MODE, PRODUCERS>(a_hi, a_hi + A_TILE_BYTES, P.img_cl, g.Cs, chan0, rows, wts, TILE_POS, TILE_POS, t);
+            const uint32_t c16 = (uint32_t)chunk_chan0(j) * ESZ / 16u;
+            produce_tiles<NC, MODE, GROUP_THREADS, 2>(a_hi, a_hi + A_TILE_BYTES, 0u, TILE_POS, TILE_POS, img16, &c16,
+                                                   plan + pbuf * TILE_POS * NC, tg);
+            if (prof_on) { const long long t1 = clock64(); t_prod += t1 - t0; t0 = t1; }
             ptx::fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&full_a[s]);
+            if (lane == 0) {
+                ptx::mbar_arrive(&full_a[s]);
+                ptx::mbar_arrive(&plan_empty[pbuf]);
+            }
+            if (prof_on) { const long long t1 = clock64(); t_sig += t1 - t0; t0 = t1; }
+        }
+        if (prof_on) {
+            P.prof[0] = t_wait; P.prof[1] = t_prod; P.prof[2] = t_sig; P.prof[3] = t_plan; P.prof[4] = n_chunks;
+            P.prof[5] = clock64() - t_begin;
+            t0 = clock64();
         }
 
         // ------------------------------------------------------------------ epilogue
@@ -146,10 +176,10 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
         ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is a whole-warp instruction
         ptx::tc_fence_after();
         if (ok) {
-            // warps w and w + 4 share TMEM lanes 32 * (w % 4) ...; they split the columns
+            // warps w, w + 4, w + 8, ... share TMEM lanes 32 * (w % 4) ...; they split the columns
             const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
             const int blocks = BN / 32;
-            for (int cb = (warp >> 2); cb < blocks; cb += 2) {
+            for (int cb = (warp >> 2); cb < blocks; cb += PRODUCER_WARPS / 4) {
                 uint32_t v[32];
                 ptx::tmem_ld_32x32(lane_base + (uint32_t)(cb * 32), v);
                 ptx::tmem_ld_wait();
@@ -168,14 +198,22 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                 }
             }
         }
+        if (prof_on) P.prof[6] = clock64() - t0;
     } else if (warp == PRODUCER_WARPS) {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
             const uint32_t idesc = ptx::instr_desc_f16(MODE == TC_F16 ? 0 : 1, TILE_POS, BN, 0, 0);
             bool ok = true;
+            const bool prof_on = P.prof != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0;
+            long long m_wa = 0, m_wb = 0, m_t0 = 0;
             for (int j = 0; j < n_chunks && ok; ++j) {
                 const int s = j % S, r = j / S;
-                if (!ptx::mbar_wait(&full_a[s], (uint32_t)(r & 1)) || !ptx::mbar_wait(&full_b[s], (uint32_t)(r & 1))) {
+                if (prof_on) m_t0 = clock64();
+                const bool got_a = ptx::mbar_wait(&full_a[s], (uint32_t)(r & 1));
+                if (prof_on) { const long long t1 = clock64(); m_wa += t1 - m_t0; m_t0 = t1; }
+                const bool got_b = got_a && ptx::mbar_wait(&full_b[s], (uint32_t)(r & 1));
+                if (prof_on) { const long long t1 = clock64(); m_wb += t1 - m_t0; P.prof[8] = m_wa; P.prof[9] = m_wb; }
+                if (!got_b) {
                     atomicExch(P.status, 103);
                     ok = false;
                     break;
@@ -200,7 +238,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
             if (ok) ptx::mma_commit(accum);
         }
         __syncwarp();
-    } else {
+    } else if (warp == PRODUCER_WARPS + 1) {
         // ------------------------------------------------------------------ TMA: weight tiles
         if (lane == 0) {
             int issued = 0;
@@ -210,7 +248,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                     atomicExch(P.status, 104);
                     break;
                 }
-                const int tap = j / P.chunks_per_tap, cc = j % P.chunks_per_tap;
+                const int tap = j % g.K, cc = j / g.K;
                 uint8_t *b_dst = sB + (size_t)s * b_stage_bytes;
                 ptx::mbar_arrive_expect_tx(&full_b[s], b_stage_bytes);
                 ptx::tma_load_4d(b_dst, &tmap_hi, &full_b[s], cc * CHUNK_C, n0, tap, grp);
@@ -224,6 +262,42 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
             }
         }
         __syncwarp();
+    }
+
+    if (warp >= PRODUCER_WARPS + 2) {
+        // ------------------------------------------------------------------ planners: one thread per position
+        // run ahead of the producers: coordinates -> plan entries, and an L1 prefetch of every corner row so
+        // that the producers' gathers hit L1
+        const int t = threadIdx.x - (PRODUCERS + 64);
+        const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + t);
+        const bool deformable = P.offset != nullptr;
+        const uint32_t row_scale = (uint32_t)g.Cs * ESZ / 16u;
+        for (int j = 0; j < n_chunks; ++j) {
+            const int pbuf = j % PLAN_BUFS;
+            const int tap = chunk_tap(j), chan0 = chunk_chan0(j);
+            const int ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
+            const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
+            const RawCoords<DIM> rc = load_coords<DIM>(g, pi, P.offset, P.mask, tap, ogi, mgi);
+            bool ok = ptx::mbar_wait(&plan_empty[pbuf], (uint32_t)(((j / PLAN_BUFS) & 1) ^ 1));
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) atomicExch(P.status, 106);
+                break;
+            }
+            PlanEntry *slot = plan + (pbuf * TILE_POS + t) * NC;
+            build_plan<DIM, MODE>(g, pi, rc, deformable, tap, row_scale, slot);
+            const uint4 *row0 = img16 + (uint32_t)chan0 * ESZ / 16u;
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                if (P.prefetch && slot[c].w != 0u) {
+                    const uint4 *ptr = row0 + slot[c].row16;
+                    asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr));
+                    if (SPLIT) asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr + 8));
+                }
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&plan_full[pbuf]);
+        }
     }
 
     ptx::tc_fence_before();
@@ -409,12 +483,29 @@ bool make_tensor_map_16bit(CUtensorMap *map, const void *base, int rank, const u
     return rc == CUDA_SUCCESS;
 }
 
+// Tuning knob read from the environment (experiments only; the defaults are what is measured and reported).
+int tuning_int(const char *name, int fallback) {
+    const char *v = getenv(name);
+    if (v == nullptr || *v == 0) return fallback;
+    const int x = atoi(v);
+    return x > 0 ? x : fallback;
+}
+
+// Cycle counters of CTA 0, filled only when TVDCN_B200_PROF is set (tuning aid; printed by the launcher).
+__device__ long long g_fwd_prof[16];
+static long long *fwd_prof_buffer() {
+    if (tuning_int("TVDCN_B200_PROF", 0) == 0) return nullptr;
+    void *addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_fwd_prof) != cudaSuccess) return nullptr;
+    return (long long *)addr;
+}
+
 // ---- launcher -----------------------------------------------------------------------------------------
 size_t fwd_tc_smem_bytes(int dim, int mode, int bn, int stages) {
     const int parts = mode == TC_SPLIT ? 2 : 1;
     const size_t stage = (size_t)(A_TILE_BYTES + bn * 128) * parts;
-    const size_t plan = (size_t)2 * (1 << dim) * TILE_POS * 8;
-    return 1024 + stages * stage + plan + (3 * stages + 1) * 8 + 16;
+    const size_t plan = (size_t)PLAN_BUFS * (1 << dim) * TILE_POS * 8;
+    return 1024 + stages * stage + plan + (3 * stages + 1 + 2 * PLAN_BUFS) * 8 + 16;
 }
 
 // Picks the dense-channel tile and the pipeline depth; returns false when the shape is not covered.
@@ -425,7 +516,7 @@ bool fwd_tc_config(int dim, int mode, int cdg, int *bn, int *stages) {
         if (cand <= cap && cdg % cand == 0) { n = cand; break; }
     if (n == 0) return false;
     int s = 0;
-    for (int cand = 4; cand >= 2; --cand)
+    for (int cand = tuning_int("TVDCN_B200_FWD_STAGES", 4); cand >= 2; --cand)
         if (fwd_tc_smem_bytes(dim, mode, n, cand) <= 227 * 1024) { s = cand; break; }
     if (s == 0) return false;
     *bn = n;
@@ -444,6 +535,14 @@ cudaError_t launch_fwd_tc_t(const GeoHost &h, const FwdParams<DIM> &P, const CUt
     dim3 grid((unsigned)((BP + TILE_POS - 1) / TILE_POS), (unsigned)(h.groups * ((h.Cd / h.groups) / P.bn)));
     LaunchScope scope("dcn_fwd_tc", stream);
     kern<<<grid, FWD_THREADS, smem, stream>>>(P, hi, lo);
+    if (P.prof != nullptr) {
+        long long h[16];
+        cudaStreamSynchronize(stream);
+        if (cudaMemcpy(h, P.prof, sizeof(h), cudaMemcpyDeviceToHost) == cudaSuccess)
+            fprintf(stderr, "[dcn_fwd_tc prof] chunks %lld: producer wait_plan %lld wait_empty %lld sample %lld signal %lld "
+                            "loop %lld epilogue %lld | mma wait_a %lld wait_b %lld (cycles, middle CTA)\n", h[4], h[3], h[0],
+                    h[1], h[2], h[5], h[6], h[8], h[9]);
+    }
     return cudaGetLastError();
 }
 
@@ -477,6 +576,8 @@ cudaError_t launch_sample_gemm_tc(const GeoHost &h, int mode, const void *img_cl
         P.bn = bn;
         P.stages = stages;
         P.chunks_per_tap = csg / CHUNK_C;
+        P.prof = fwd_prof_buffer();
+        P.prefetch = tuning_int("TVDCN_B200_PREFETCH", 0);
         if (mode == TC_BF16) return launch_fwd_tc_t<DIM, TC_BF16>(h, P, hi, lo, stream);
         if (mode == TC_F16) return launch_fwd_tc_t<DIM, TC_F16>(h, P, hi, lo, stream);
         return launch_fwd_tc_t<DIM, TC_SPLIT>(h, P, hi, lo, stream);

@@ -41,21 +41,24 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t by
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
 }
+// Upper bound, in nanoseconds, on how long one try_wait may sleep in hardware before it reports back.
+constexpr uint32_t kSuspendHintNs = 20000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, P;\n\t"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: about a second of polling at most, then gives up.
-constexpr uint32_t kMaxPolls = 1u << 22;
+// Bounded wait: at most 2^17 polls (each sleeps up to the hint above: a few seconds in the worst case, far
+// beyond any legitimate wait), then gives up.
+constexpr uint32_t kMaxPolls = 1u << 17;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     for (uint32_t i = 0; i < kMaxPolls; ++i)
         if (mbar_try_wait(bar, parity)) return true;

@@ -67,9 +67,8 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
     const uint32_t b_stage_bytes = b_part_bytes * PARTS;
     uint8_t *sA = smem;
     uint8_t *sB = sA + (size_t)S * a_stage_bytes;
-    int *plan_rows = reinterpret_cast<int *>(sB + (size_t)S * b_stage_bytes);   // [2][NS][NC][64]
-    float *plan_wts = reinterpret_cast<float *>(plan_rows + 2 * NS * NC * WG_POS);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(plan_wts + 2 * NS * NC * WG_POS);
+    PlanEntry *plan = reinterpret_cast<PlanEntry *>(sB + (size_t)S * b_stage_bytes);   // [2][NS * 64][NC]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(plan + 2 * NS * NC * WG_POS);
     uint64_t *full_s = bars;           // sampled tiles written
     uint64_t *full_d = bars + S;       // dense tiles landed
     uint64_t *empty = bars + 2 * S;
@@ -117,53 +116,62 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
         const int my_sub = t / WG_POS, my_slot = t % WG_POS;     // plan entry this thread fills
         const int my_kt = kt0 + my_sub;
         const bool my_sub_ok = my_sub < NS && my_kt < sub_total;
-        const int my_tap = my_sub_ok ? my_kt / P.chunks_per_tap : 0;
-        const int my_chan0 = grp * g.csg + (my_sub_ok ? my_kt % P.chunks_per_tap : 0) * CHUNK_C;
+        // column blocks are ordered channel chunk outermost, tap innermost: the blocks of one CTA share an
+        // image slab, which stays in L1
+        const int my_tap = my_sub_ok ? my_kt % g.K : 0;
+        const int my_chan0 = grp * g.csg + (my_sub_ok ? my_kt / g.K : 0) * CHUNK_C;
         const int my_og = g.og > 0 ? my_chan0 / g.cs_per_og : 0;
         const int my_mg = g.mg > 0 ? my_chan0 / g.cs_per_mg : 0;
+        const bool deformable = P.offset != nullptr;
+        constexpr uint32_t ESZ = SPLIT ? 4 : 2;
+        const uint32_t row_scale = (uint32_t)g.Cs * ESZ / 16u;
+        const uint4 *img16 = reinterpret_cast<const uint4 *>(P.img_cl);
+        __shared__ uint32_t chan16_s[4];
+        if (my_slot == 0 && my_sub < NS) chan16_s[my_sub] = (uint32_t)my_chan0 * ESZ / 16u;
+        // position of this thread's plan entry in stage i
+        auto position_of = [&](int i) {
+            PosInfo<DIM> pi;
+            const int pc = chunk_begin + i;
+            const int p = (pc % P.chunks_per_image) * WG_POS + my_slot;
+            pi.valid = my_sub_ok && i < n_stages && p < g.P;
+            pi.b = pc / P.chunks_per_image;
+            pi.p = pi.valid ? p : 0;
+            decode_in_image<DIM>(g, pi);
+            return pi;
+        };
+        PosInfo<DIM> pi = position_of(0);
+        if (my_sub < NS) {
+            const RawCoords<DIM> rc0 = load_coords<DIM>(g, pi, P.offset, P.mask, my_tap, my_og, my_mg);
+            build_plan<DIM, MODE>(g, pi, rc0, deformable, my_tap, row_scale, plan + (my_sub * WG_POS + my_slot) * NC);
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         bool ok = true;
         for (int i = 0; i < n_stages; ++i) {
             const int s = i % S, r = i / S;
-            const int pc = chunk_begin + i;
-            const int b = pc / P.chunks_per_image;
-            const int p0 = (pc % P.chunks_per_image) * WG_POS;
             const int pb = i & 1;
-            if (my_sub < NS) {
-                PosInfo<DIM> pi;
-                const int p = p0 + my_slot;
-                pi.valid = my_sub_ok && p < g.P;
-                pi.b = b;
-                pi.p = pi.valid ? p : 0;
-                int rem = pi.p;
-#pragma unroll
-                for (int a = DIM - 1; a >= 0; --a) {
-                    const int c = rem % g.grid[a];
-                    rem /= g.grid[a];
-                    pi.base[a] = c * g.stride[a] - g.pad[a];
-                }
-                PlanView<DIM> pv{plan_rows + (pb * NS + my_sub) * NC * WG_POS,
-                                 plan_wts + (pb * NS + my_sub) * NC * WG_POS};
-                fill_plan<DIM>(g, pi, P.offset, P.mask, my_tap, my_og, my_mg, my_slot, WG_POS, pv);
-            }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            // next stage's coordinates are fetched now, its plan is written after this stage's sampling
+            RawCoords<DIM> rcn;
+            PosInfo<DIM> pin = position_of(i + 1);
+            if (my_sub < NS && i + 1 < n_stages) rcn = load_coords<DIM>(g, pin, P.offset, P.mask, my_tap, my_og, my_mg);
             if (ok && !ptx::mbar_wait(&empty[s], (uint32_t)((r & 1) ^ 1))) {
                 atomicExch(P.status, 201);
                 ok = false;
             }
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) continue;
-            uint8_t *b_hi = sB + (size_t)s * b_stage_bytes;
-            for (int sub = 0; sub < NS; ++sub) {
-                const int kt = kt0 + sub;
-                const int chan0 = grp * g.csg + (kt < sub_total ? kt % P.chunks_per_tap : 0) * CHUNK_C;
-                produce_tile<NC, MODE, WG_PRODUCERS>(b_hi + sub * WG_B_TILE, b_hi + b_part_bytes + sub * WG_B_TILE,
-                                                     P.img_cl, g.Cs, chan0,
-                                                     plan_rows + (pb * NS + sub) * NC * WG_POS,
-                                                     plan_wts + (pb * NS + sub) * NC * WG_POS, WG_POS, WG_POS, t);
+            if (ok) {
+                uint8_t *b_hi = sB + (size_t)s * b_stage_bytes;
+                produce_tiles<NC, MODE, WG_PRODUCERS>(b_hi, b_hi + b_part_bytes, WG_B_TILE, WG_POS, NS * WG_POS, img16,
+                                                      chan16_s, plan + pb * NS * WG_POS * NC, t);
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&full_s[s]);
             }
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&full_s[s]);
+            if (i + 1 < n_stages) {
+                if (my_sub < NS)
+                    build_plan<DIM, MODE>(g, pin, rcn, deformable, my_tap, row_scale,
+                                          plan + (((pb ^ 1) * NS + my_sub) * WG_POS + my_slot) * NC);
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+            }
         }
 
         // ------------------------------------------------------------------ epilogue: atomics into gw
@@ -188,8 +196,8 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
                     const int kt = kt0 + sub;
                     const int dl = d0 + m * 128 + lane_q * 32 + lane;   // dense channel within the group
                     if (kt < sub_total && dl < g.cdg) {
-                        const int tap = kt / P.chunks_per_tap;
-                        const int sl0 = (kt % P.chunks_per_tap) * CHUNK_C + (col0 % 64);
+                        const int tap = kt % g.K;
+                        const int sl0 = (kt / g.K) * CHUNK_C + (col0 % 64);
                         float *dst = P.gw + ((int64_t)(grp * g.cdg + dl) * g.csg + sl0) * g.K + tap;
 #pragma unroll
                         for (int e = 0; e < 32; ++e) atomicAdd(dst + (int64_t)e * g.K, __uint_as_float(v[e]));
@@ -298,7 +306,7 @@ bool wgrad_tc_config(int dim, int mode, int cdg, int P, int *n_sub, int *m_tiles
     int ns = mode == TC_SPLIT ? 2 : 4;
     if (dim == 3 && mode != TC_SPLIT) ns = 4;
     int s = 0;
-    for (int cand = 4; cand >= 2; --cand)
+    for (int cand = tuning_int("TVDCN_B200_WG_STAGES", 2); cand >= 2; --cand)
         if (wgrad_smem_bytes(dim, mode, ns, mt, cand) <= 227 * 1024) { s = cand; break; }
     if (s == 0) return false;
     *n_sub = ns;
