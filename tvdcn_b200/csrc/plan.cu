@@ -25,7 +25,8 @@ const char *tc_common(const tvdcn_problem *p, const GeoHost &g) {
     if (cdg % 64 != 0) return "dense channels per group must be a multiple of 64";
     if (g.og > 0 && (g.Cs / g.og) % 64 != 0) return "channels per offset group must be a multiple of 64";
     if (g.mg > 0 && (g.Cs / g.mg) % 64 != 0) return "channels per mask group must be a multiple of 64";
-    if ((long long)g.B * g.S >= (1LL << 31) || (long long)g.B * g.P >= (1LL << 31)) return "too many image rows";
+    if ((long long)g.B * g.S * g.Cs >= (1LL << 31) || (long long)g.B * g.P >= (1LL << 31))
+        return "sampled image has 2^31 elements or more (32-bit element offsets)";
     return nullptr;
 }
 

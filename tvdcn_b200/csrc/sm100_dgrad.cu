@@ -53,9 +53,20 @@ constexpr int DG_TMEM_COLS = 512;
 
 // where one corner of one position scatters to (row of the channels-last image) and with what factor
 struct ScatterInfo {
-    int row;
+    uint32_t off;   // row * Cs: element offset of the row in the channels-last image
     float scale;
 };
+
+// predicated form: no branch around the reduction
+__device__ __forceinline__ void red_add_v4_if(bool p, float *addr, float a, float b, float c, float d) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred q;\n\t"
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q red.global.add.v4.f32 [%0], {%1, %2, %3, %4};\n\t"
+        "}\n" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d), "r"((int)p)
+        : "memory");
+}
 
 __device__ __forceinline__ void red_add_v4(float *addr, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
@@ -120,7 +131,8 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
     const Geo<DIM> &g = P.g;
 
     extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // align by offset, not by integer round-trip, so that the compiler keeps these as shared-memory pointers
+    uint8_t *smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     const int RC = P.rc, NB = P.nb, BS = P.b_stages;
     const int ncol = NB * 64;                       // columns per accumulator
     const int NQ = DG_TMEM_COLS / ncol;             // accumulators in the ring (8 or 4)
@@ -137,7 +149,8 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
     uint64_t *t_empty = t_full + 8;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(t_empty + 8);
     // per-epilogue-warp staging for the transposed scatter: [32 pos][32 ch] f32 + [32 pos][NC] corner info
-    float *stage_g = reinterpret_cast<float *>((reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));
+    float *stage_g = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(tmem_slot + 4) +
+                                               ((16u - (ptx::smem_u32(tmem_slot + 4) & 15u)) & 15u));
     ScatterInfo *stage_c = reinterpret_cast<ScatterInfo *>(stage_g + DG_EPI_WARPS * 32 * 32);
     float *stage_d = reinterpret_cast<float *>(stage_c + DG_EPI_WARPS * 32 * NC);   // [warp][32 pos][NC] dot products
 
@@ -305,7 +318,7 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
 #pragma unroll
                 for (int c = 0; c < NC; ++c) {
                     ScatterInfo si;
-                    si.row = rowi[c];
+                    si.off = (uint32_t)rowi[c] * (uint32_t)g.Cs;
                     si.scale = okc[c] ? mval * wc[c] : 0.f;
                     cs[lane * NC + c] = si;
                 }
@@ -323,7 +336,7 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                             const int pos = (it0 + i) * 8 + p8;
 #pragma unroll
                             for (int c = 0; c < NC; ++c)
-                                cl[i][c].load(img + (int64_t)cs[pos * NC + c].row * g.Cs + ch0 + q4 * 8);
+                                cl[i][c].load(img + cs[pos * NC + c].off + (uint32_t)(ch0 + q4 * 8));
                         }
 #pragma unroll
                         for (int i = 0; i < ITB; ++i) {
@@ -351,9 +364,8 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
 #pragma unroll
                         for (int c = 0; c < NC; ++c) {
                             const ScatterInfo si = cs[pos * NC + c];
-                            if (si.scale != 0.f)
-                                red_add_v4(dst0 + (int64_t)si.row * g.Cs, qv.x * si.scale, qv.y * si.scale, qv.z * si.scale,
-                                           qv.w * si.scale);
+                            red_add_v4_if(si.scale != 0.f, dst0 + si.off, qv.x * si.scale, qv.y * si.scale, qv.z * si.scale,
+                                          qv.w * si.scale);
                         }
                     }
                 }

@@ -59,7 +59,8 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
     const Geo<DIM> &g = P.g;
 
     extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // align by offset, not by integer round-trip, so that the compiler keeps these as shared-memory pointers
+    uint8_t *smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
     const int S = P.stages;
     const int NS = P.n_sub, MT = P.m_tiles;
     const uint32_t a_stage_bytes = (uint32_t)(MT * PARTS * WG_A_TILE);   // [m][part]
