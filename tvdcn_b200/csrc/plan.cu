@@ -54,7 +54,7 @@ Plan plan_forward(const tvdcn_problem *p) {
     const int mode = tc_mode_of(p->dtype);
     const size_t es = p->dtype == TVDCN_F32 ? 4 : 2;
     const size_t nw = (size_t)g.Cd * (g.Cs / g.groups) * g.K;
-    int bn = 0, st = 0;
+    int bn = 0, st = 0, gbufs = 0;
     if (why == nullptr && !p->transposed) {
         if (fwd_tc_config(g.dim, mode, g.Cd / g.groups, &bn, &st)) {
             pl.tensor = pl.tc_sg = true;
@@ -65,7 +65,7 @@ Plan plan_forward(const tvdcn_problem *p) {
             why = "no tile configuration fits";
         }
     } else if (why == nullptr) {
-        if (dgrad_tc_config(mode, g.Cd / g.groups, g.Cs / g.groups, &bn, &st)) {
+        if (dgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.Cs / g.groups, &bn, &st, &gbufs)) {
             pl.tensor = pl.tc_gs = true;
             take_scatter_buffers(pl, b, p, g, true);
         } else {
@@ -91,7 +91,7 @@ Plan plan_backward(const tvdcn_problem *p, bool want_input, bool want_weight, bo
     want_offset = want_offset && g.og > 0;
     want_mask = want_mask && g.mg > 0;
     if (why == nullptr) {
-        int bn = 0, st = 0, ns = 0, mt = 0;
+        int bn = 0, st = 0, ns = 0, mt = 0, gbufs = 0;
         // transposed backward: grad_input is a sample -> GEMM over grad_output
         if (p->transposed && want_input && fwd_tc_config(g.dim, mode, g.Cd / g.groups, &bn, &st)) {
             pl.tc_sg = true;
@@ -107,7 +107,7 @@ Plan plan_backward(const tvdcn_problem *p, bool want_input, bool want_weight, bo
         }
         // conv: scatter into grad_input + coordinate gradients; transposed: coordinate gradients only
         const bool scatter = !p->transposed && want_input;
-        if ((scatter || want_offset || want_mask) && dgrad_tc_config(mode, g.Cd / g.groups, g.Cs / g.groups, &bn, &st)) {
+        if ((scatter || want_offset || want_mask) && dgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.Cs / g.groups, &bn, &st, &gbufs)) {
             pl.tc_gs = true;
             take_scatter_buffers(pl, b, p, g, scatter);
         }

@@ -57,7 +57,7 @@ bool wgrad_tc_config(int dim, int mode, int cdg, int P, int *n_sub, int *m_tiles
 cudaError_t launch_sample_wgrad_tc(const GeoHost &g, int mode, const void *dense_hi, const void *dense_lo,
                                    const void *img_cl, const float *offset, const float *mask, float *gw,
                                    int *status, cudaStream_t stream);
-bool dgrad_tc_config(int mode, int cdg, int csg, int *nb, int *b_stages);
+bool dgrad_tc_config(int dim, int mode, int cdg, int csg, int *nb, int *b_stages, int *g_bufs);
 cudaError_t launch_gemm_scatter_tc(const GeoHost &g, int mode, const void *dense_cl_hi, const void *dense_cl_lo,
                                    const void *w_kd_hi, const void *w_kd_lo, const void *img_cl, const float *offset,
                                    const float *mask, float *img_grad_cl, float *goff, float *gmask, int *status,

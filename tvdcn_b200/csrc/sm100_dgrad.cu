@@ -15,11 +15,14 @@
 //       the position tile stay resident in shared memory while the CTA walks the column blocks;
 //   B = weights packed [g][tap][s'][d'] (K-major, TMA ring);
 //   D = a ring of accumulators in tensor memory, so the MMA of later column blocks overlaps the epilogue.
-// Epilogue (8 warps, thread = position, two warps share a lane quadrant and split the columns): one dot
-// product <col, image corner> per corner gives both coordinate gradients; the scatter uses 16-byte vector
-// reductions into a channels-last f32 image (one red per 4 channels instead of one atomic per element).
+// Epilogue: eight scatter warps (two per TMEM lane quadrant, splitting the columns) read the accumulator,
+// stage it transposed in shared memory and scatter it with 16-byte vector reductions into a channels-last
+// f32 image, 8 lanes per row; eight coordinate warps read the same staged tile, gather the image corners
+// with 4 lanes per row and reduce one dot product <col, corner row> per corner, which gives both
+// coordinate gradients.
 //
-// Warp roles (320 threads): warps 0-7 epilogue, warp 8 MMA issue + TMEM owner, warp 9 TMA.
+// Warp roles (576 threads): warps 0-7 scatter, warps 8-15 coordinate gradients, warp 16 MMA issue + TMEM
+// owner, warp 17 TMA.
 #include <algorithm>
 #include <type_traits>
 
@@ -42,12 +45,15 @@ struct DgradParams {
     int rc;                 // reduction chunks: cdg / 64
     int b_stages;
     int chunks_per_tap;     // csg / 64
+    int g_bufs;             // staged-tile buffers per warp pair: 1 or 2
 };
 
 namespace {
 
-constexpr int DG_EPI_WARPS = 8;
-constexpr int DG_THREADS = DG_EPI_WARPS * 32 + 64;
+constexpr int DG_PAIRS = 8;            // scatter warp + coordinate warp per (lane quadrant, column half)
+constexpr int DG_MMA_WARP = 2 * DG_PAIRS;
+constexpr int DG_TMA_WARP = 2 * DG_PAIRS + 1;
+constexpr int DG_THREADS = (2 * DG_PAIRS + 2) * 32;
 constexpr int DG_A_TILE = 128 * 128;   // [128 pos][64 d] 16-bit
 constexpr int DG_TMEM_COLS = 512;
 
@@ -117,6 +123,71 @@ struct CornerLoad {
     }
 };
 
+// Sampling geometry of one (position, tap, offset group, mask group), kept by an epilogue thread.
+template <int DIM>
+struct TapGeometry {
+    int fl[DIM];
+    float fr[DIM];
+    float mval = 1.f;
+    int tap = -1, og = -1, mtap = -1, mg = -1;
+};
+
+// corner c of the 2^DIM cell: in bounds?, row of the channels-last image, interpolation weight
+template <int DIM>
+__device__ __forceinline__ void corner_of(const Geo<DIM> &g, const PosInfo<DIM> &pi, const TapGeometry<DIM> &tg,
+                                          bool deformable, int c, bool &ok, int &rowi, float &w) {
+    ok = pi.valid && (deformable || c == 0);
+    int flat = 0;
+    w = 1.f;
+#pragma unroll
+    for (int a = 0; a < DIM; ++a) {
+        const int bit = (c >> (DIM - 1 - a)) & 1;
+        const int i = (int)((unsigned)tg.fl[a] + (unsigned)bit);
+        ok = ok && ((unsigned)i < (unsigned)g.img[a]);
+        flat = flat * g.img[a] + i;
+        w *= bit ? tg.fr[a] : (1.f - tg.fr[a]);
+    }
+    rowi = ok ? pi.b * g.S + flat : 0;
+    if (!ok) w = 0.f;
+}
+
+template <int DIM>
+__device__ __forceinline__ void load_point(const Geo<DIM> &g, const PosInfo<DIM> &pi, const float *__restrict__ offset,
+                                           int tap, int ogi, TapGeometry<DIM> &tg) {
+    int r = tap, tc[DIM];
+#pragma unroll
+    for (int a = DIM - 1; a >= 0; --a) {
+        tc[a] = r % g.ker[a];
+        r /= g.ker[a];
+    }
+#pragma unroll
+    for (int a = 0; a < DIM; ++a) {
+        const int base = pi.base[a] + tc[a] * g.dil[a];
+        if (offset != nullptr && pi.valid) {
+            const float o = __ldg(offset + ((((int64_t)pi.b * g.og + ogi) * g.K + tap) * DIM + a) * (int64_t)g.P + pi.p);
+            const float pos = (float)base + o;
+            const float f = floorf(pos);
+            tg.fl[a] = (int)f;
+            tg.fr[a] = pos - f;
+        } else {
+            tg.fl[a] = base;
+            tg.fr[a] = 0.f;
+        }
+    }
+    tg.tap = tap;
+    tg.og = ogi;
+}
+
+template <int DIM>
+__device__ __forceinline__ void load_mask(const Geo<DIM> &g, const PosInfo<DIM> &pi, const float *__restrict__ mask,
+                                          int tap, int mgi, TapGeometry<DIM> &tg) {
+    tg.mval = (mask != nullptr && pi.valid)
+                  ? __ldg(mask + (((int64_t)pi.b * g.mg + mgi) * g.K + tap) * (int64_t)g.P + pi.p)
+                  : 1.f;
+    tg.mtap = tap;
+    tg.mg = mgi;
+}
+
 template <int DIM, int MODE>
 __global__ void __launch_bounds__(DG_THREADS, 1)
 dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMap tmap_a_hi,
@@ -126,8 +197,6 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
     constexpr bool SPLIT = MODE == TC_SPLIT;
     constexpr int PARTS = SPLIT ? 2 : 1;
     using TI = typename std::conditional<SPLIT, float, typename std::conditional<MODE == TC_F16, __half, __nv_bfloat16>::type>::type;
-    constexpr int ESZ = SPLIT ? 4 : 2;
-    constexpr int PS = (256 / (NC * ESZ)) < 32 ? (256 / (NC * ESZ)) : 32;  // channels per register piece
     const Geo<DIM> &g = P.g;
 
     extern __shared__ uint8_t smem_raw[];
@@ -141,24 +210,28 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
     const uint32_t b_stage_bytes = b_part_bytes * PARTS;
     uint8_t *sA = smem;
     uint8_t *sB = sA + a_bytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sB + (size_t)BS * b_stage_bytes);
+    // epilogue staging, per scatter warp: two [32 pos][32 ch] f32 tiles (double buffer shared with the paired
+    // coordinate warp), scatter info [32][NC]; per coordinate warp: row offsets [32][NC] and dots [32][NC]
+    float *stage_g = reinterpret_cast<float *>(sB + (size_t)BS * b_stage_bytes);          // [8][g_bufs][32*32]
+    ScatterInfo *stage_c = reinterpret_cast<ScatterInfo *>(stage_g + DG_PAIRS * P.g_bufs * 1024);  // [8][32*NC]
+    uint32_t *stage_r = reinterpret_cast<uint32_t *>(stage_c + DG_PAIRS * 32 * NC);         // [8][32*NC]
+    float *stage_d = reinterpret_cast<float *>(stage_r + DG_PAIRS * 32 * NC);               // [8][32*NC]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(stage_d + DG_PAIRS * 32 * NC);
     uint64_t *a_full = bars;
     uint64_t *b_full = bars + 1;
     uint64_t *b_empty = b_full + BS;
     uint64_t *t_full = b_empty + BS;
     uint64_t *t_empty = t_full + 8;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(t_empty + 8);
-    // per-epilogue-warp staging for the transposed scatter: [32 pos][32 ch] f32 + [32 pos][NC] corner info
-    float *stage_g = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(tmem_slot + 4) +
-                                               ((16u - (ptx::smem_u32(tmem_slot + 4) & 15u)) & 15u));
-    ScatterInfo *stage_c = reinterpret_cast<ScatterInfo *>(stage_g + DG_EPI_WARPS * 32 * 32);
-    float *stage_d = reinterpret_cast<float *>(stage_c + DG_EPI_WARPS * 32 * NC);   // [warp][32 pos][NC] dot products
+    uint64_t *g_full = t_empty + 8;       // [8 pairs][2]: scatter warp -> coordinate warp: tile staged
+    uint64_t *g_empty = g_full + 16;      // [8 pairs][2]: coordinate warp -> scatter warp: tile consumed
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(g_empty + 16);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int grp = blockIdx.y;
     const long long m0 = (long long)blockIdx.x * TILE_POS;
-    const int blocks_per_tap = P.chunks_per_tap / NB;
-    const int n_blocks = g.K * blocks_per_tap;
+    const int n_blocks = g.K * (P.chunks_per_tap / NB);
+    const bool want_coord = P.goff != nullptr || P.gmask != nullptr;
+    const bool deformable = P.offset != nullptr;
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(a_full, 1);
@@ -168,11 +241,15 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
         }
         for (int q = 0; q < 8; ++q) {
             ptx::mbar_init(&t_full[q], 1);
-            ptx::mbar_init(&t_empty[q], DG_EPI_WARPS);
+            ptx::mbar_init(&t_empty[q], DG_PAIRS);
+        }
+        for (int i = 0; i < 16; ++i) {
+            ptx::mbar_init(&g_full[i], 1);
+            ptx::mbar_init(&g_empty[i], 1);
         }
         ptx::fence_mbar_init();
     }
-    if (warp == DG_EPI_WARPS + 1 && lane == 0) {
+    if (warp == DG_TMA_WARP && lane == 0) {
         ptx::prefetch_tmap(&tmap_a_hi);
         ptx::prefetch_tmap(&tmap_b_hi);
         if (SPLIT) {
@@ -180,7 +257,7 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
             ptx::prefetch_tmap(&tmap_b_lo);
         }
     }
-    if (warp == DG_EPI_WARPS) {
+    if (warp == DG_MMA_WARP) {
         ptx::tmem_alloc(tmem_slot, DG_TMEM_COLS);
         ptx::tmem_relinquish();
     }
@@ -189,122 +266,56 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < DG_EPI_WARPS) {
-        // ------------------------------------------------------------------ epilogue
+    if (warp < DG_PAIRS) {
+        // ------------------------------------------------------------------ scatter warps
+        // TMEM -> registers -> shared tile (handed to the paired coordinate warp) -> vector reductions
         const int lane_q = warp & 3, half = warp >> 2;
         const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + lane_q * 32 + lane);
-        const bool deformable = P.offset != nullptr;
-        const bool want_coord = P.goff != nullptr || P.gmask != nullptr;
-        const TI *img = reinterpret_cast<const TI *>(P.img_cl);
-        int fl[DIM];
-        float fr[DIM];
-        float mval = 1.f;
-        int cur_tap = -1, cur_og = -1, cur_mtap = -1, cur_mg = -1;
-        float go_sum[DIM], gm_sum = 0.f;
-#pragma unroll
-        for (int a = 0; a < DIM; ++a) go_sum[a] = 0.f;
-
-        auto flush_off = [&]() {
-            if (P.goff != nullptr && cur_tap >= 0 && pi.valid) {
-#pragma unroll
-                for (int a = 0; a < DIM; ++a)
-                    atomicAdd(P.goff + ((((int64_t)pi.b * g.og + cur_og) * g.K + cur_tap) * DIM + a) * (int64_t)g.P + pi.p,
-                              go_sum[a]);
-            }
-#pragma unroll
-            for (int a = 0; a < DIM; ++a) go_sum[a] = 0.f;
-        };
-        auto flush_mask = [&]() {
-            if (P.gmask != nullptr && cur_mtap >= 0 && pi.valid)
-                atomicAdd(P.gmask + (((int64_t)pi.b * g.mg + cur_mg) * g.K + cur_mtap) * (int64_t)g.P + pi.p, gm_sum);
-            gm_sum = 0.f;
-        };
-
+        TapGeometry<DIM> tg;
+        ScatterInfo *cs = stage_c + warp * 32 * NC;
+        const bool scatter = P.img_grad_cl != nullptr;
+        int k = 0;  // chunks handled so far: selects the staging buffer
         bool ok = true;
-        for (int blk = 0; blk < n_blocks; ++blk) {
+        for (int blk = 0; blk < n_blocks && ok; ++blk) {
             const int q = blk % NQ;
             const int tap = blk % g.K;
             const int cc0 = (blk / g.K) * NB;
-            if (ok && !ptx::mbar_wait(&t_full[q], (uint32_t)((blk / NQ) & 1))) {
-                atomicExch(P.status, 301);
-                ok = false;
-            }
+            ok = ptx::mbar_wait(&t_full[q], (uint32_t)((blk / NQ) & 1));
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            if (!ok) {
+                if (lane == 0) atomicExch(P.status, 301);
+                break;
+            }
             ptx::tc_fence_after();
-            for (int ci = 0; ci < NB; ++ci) {
+            for (int ci = 0; ci < NB; ++ci, ++k) {
                 const int chan0 = grp * g.csg + (cc0 + ci) * CHUNK_C;
-                const int ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
-                const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
-                if (tap != cur_tap || ogi != cur_og) {
-                    flush_off();
-                    cur_tap = tap;
-                    cur_og = ogi;
-                    int r = tap, tc[DIM];
-#pragma unroll
-                    for (int a = DIM - 1; a >= 0; --a) {
-                        tc[a] = r % g.ker[a];
-                        r /= g.ker[a];
-                    }
-#pragma unroll
-                    for (int a = 0; a < DIM; ++a) {
-                        const int base = pi.base[a] + tc[a] * g.dil[a];
-                        if (deformable && pi.valid) {
-                            const float o = __ldg(P.offset + ((((int64_t)pi.b * g.og + ogi) * g.K + tap) * DIM + a) *
-                                                                 (int64_t)g.P + pi.p);
-                            const float pos = (float)base + o;
-                            const float f = floorf(pos);
-                            fl[a] = (int)f;
-                            fr[a] = pos - f;
-                        } else {
-                            fl[a] = base;
-                            fr[a] = 0.f;
-                        }
-                    }
-                }
-                if (tap != cur_mtap || mgi != cur_mg) {
-                    flush_mask();
-                    cur_mtap = tap;
-                    cur_mg = mgi;
-                    mval = (P.mask != nullptr && pi.valid)
-                               ? __ldg(P.mask + (((int64_t)pi.b * g.mg + mgi) * g.K + tap) * (int64_t)g.P + pi.p)
-                               : 1.f;
-                }
-                // corner geometry of this (position, tap, offset group)
-                int64_t row[NC];
-                int rowi[NC];
-                float wc[NC];
-                bool okc[NC];
-#pragma unroll
-                for (int c = 0; c < NC; ++c) {
-                    bool v = pi.valid && (deformable || c == 0);
-                    int flat = 0;
-                    float w = 1.f;
-#pragma unroll
-                    for (int a = 0; a < DIM; ++a) {
-                        const int bit = (c >> (DIM - 1 - a)) & 1;
-                        const int i = (int)((unsigned)fl[a] + (unsigned)bit);
-                        v = v && ((unsigned)i < (unsigned)g.img[a]);
-                        flat = flat * g.img[a] + i;
-                        w *= bit ? fr[a] : (1.f - fr[a]);
-                    }
-                    okc[c] = v;
-                    wc[c] = v ? w : 0.f;
-                    rowi[c] = v ? pi.b * g.S + flat : 0;
-                    row[c] = (int64_t)rowi[c] * g.Cs;
-                }
-                // this warp's 32 columns of the chunk
+                const int ch0 = chan0 + half * 32;
+                const int buf = k % P.g_bufs;
+                float *gs = stage_g + (warp * P.g_bufs + buf) * 1024;
                 uint32_t raw[32];
                 ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(lane_q * 32) << 16) + (uint32_t)(q * ncol + ci * 64 + half * 32),
                                    raw);
+                if (scatter) {
+                    const int ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
+                    const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
+                    if (tap != tg.tap || ogi != tg.og) load_point<DIM>(g, pi, P.offset, tap, ogi, tg);
+                    if (tap != tg.mtap || mgi != tg.mg) load_mask<DIM>(g, pi, P.mask, tap, mgi, tg);
+                }
                 ptx::tmem_ld_wait();
-                // Transpose through shared memory: afterwards a few lanes share one position and cover a
-                // contiguous piece of an image row, so a warp-wide load or vector reduction touches 4-8 rows
-                // instead of 32 (thread = position would make every access a 32-row gather).
-                float *gs = stage_g + warp * 32 * 32;
-                ScatterInfo *cs = stage_c + warp * 32 * NC;
-                float *ds_ = stage_d + warp * 32 * NC;
-                const int ch0 = chan0 + half * 32;
+                if (ci == NB - 1) {
+                    // the accumulator is in registers: hand it back to the MMA warp right away
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&t_empty[q]);
+                }
+                if (want_coord) {
+                    ok = ptx::mbar_wait(&g_empty[warp * 2 + buf], (uint32_t)(((k / P.g_bufs) & 1) ^ 1));
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) {
+                        if (lane == 0) atomicExch(P.status, 306);
+                        break;
+                    }
+                }
                 __syncwarp();
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -315,28 +326,125 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                     qv.w = __uint_as_float(raw[4 * i + 3]);
                     *reinterpret_cast<float4 *>(gs + lane * 32 + ((i ^ (lane & 7)) << 2)) = qv;
                 }
+                if (scatter) {
 #pragma unroll
-                for (int c = 0; c < NC; ++c) {
-                    ScatterInfo si;
-                    si.off = (uint32_t)rowi[c] * (uint32_t)g.Cs;
-                    si.scale = okc[c] ? mval * wc[c] : 0.f;
-                    cs[lane * NC + c] = si;
+                    for (int c = 0; c < NC; ++c) {
+                        bool okc;
+                        int rowi;
+                        float w;
+                        corner_of<DIM>(g, pi, tg, deformable, c, okc, rowi, w);
+                        ScatterInfo si;
+                        si.off = (uint32_t)rowi * (uint32_t)g.Cs;
+                        si.scale = tg.mval * w;
+                        cs[lane * NC + c] = si;
+                    }
                 }
                 __syncwarp();
-                if (want_coord) {
-                    // 4 lanes per position, 8 channels each: dot products <col, corner row> reduced over the 4 lanes
-                    const int q4 = lane & 3, p8 = lane >> 2;
-                    // loads of ITB iterations (8 positions each) are issued together so that their latency overlaps
+                if (want_coord && lane == 0) ptx::mbar_arrive(&g_full[warp * 2 + buf]);
+                if (scatter) {
+                    // 8 lanes cover the 128 contiguous bytes of one image row: a warp-wide vector reduction
+                    // touches 4 rows (thread = position would touch 32)
+                    const int quad = lane & 7;
+                    float *dst0 = P.img_grad_cl + ch0 + quad * 4;
+#pragma unroll 2
+                    for (int it = 0; it < 8; ++it) {
+                        const int pos = it * 4 + (lane >> 3);
+                        const float4 qv = *reinterpret_cast<const float4 *>(gs + pos * 32 + ((quad ^ (pos & 7)) << 2));
+#pragma unroll
+                        for (int c = 0; c < NC; ++c) {
+                            const ScatterInfo si = cs[pos * NC + c];
+                            red_add_v4_if(si.scale != 0.f, dst0 + si.off, qv.x * si.scale, qv.y * si.scale, qv.z * si.scale,
+                                          qv.w * si.scale);
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp < 2 * DG_PAIRS) {
+        // ------------------------------------------------------------------ coordinate warps
+        // read the tile its scatter warp staged, gather the image corners with 4 lanes per position and
+        // turn <col, corner row> dot products into grad_offset / grad_mask sums
+        if (want_coord) {
+            const int pair = warp - DG_PAIRS;
+            const int lane_q = pair & 3, half = pair >> 2;
+            const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + lane_q * 32 + lane);
+            const TI *img = reinterpret_cast<const TI *>(P.img_cl);
+            TapGeometry<DIM> tg;
+            uint32_t *rs = stage_r + pair * 32 * NC;
+            float *ds_ = stage_d + pair * 32 * NC;
+            float go_sum[DIM], gm_sum = 0.f;
+#pragma unroll
+            for (int a = 0; a < DIM; ++a) go_sum[a] = 0.f;
+            auto flush_off = [&]() {
+                if (P.goff != nullptr && tg.tap >= 0 && pi.valid) {
+#pragma unroll
+                    for (int a = 0; a < DIM; ++a)
+                        atomicAdd(P.goff + ((((int64_t)pi.b * g.og + tg.og) * g.K + tg.tap) * DIM + a) * (int64_t)g.P + pi.p,
+                                  go_sum[a]);
+                }
+#pragma unroll
+                for (int a = 0; a < DIM; ++a) go_sum[a] = 0.f;
+            };
+            auto flush_mask = [&]() {
+                if (P.gmask != nullptr && tg.mtap >= 0 && pi.valid)
+                    atomicAdd(P.gmask + (((int64_t)pi.b * g.mg + tg.mg) * g.K + tg.mtap) * (int64_t)g.P + pi.p, gm_sum);
+                gm_sum = 0.f;
+            };
+            const int q4 = lane & 3, p8 = lane >> 2;
+            int k = 0;
+            bool ok = true;
+            for (int blk = 0; blk < n_blocks && ok; ++blk) {
+                const int tap = blk % g.K;
+                const int cc0 = (blk / g.K) * NB;
+                for (int ci = 0; ci < NB; ++ci, ++k) {
+                    const int chan0 = grp * g.csg + (cc0 + ci) * CHUNK_C;
+                    const int ch0 = chan0 + half * 32;
+                    const int ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
+                    const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
+                    if (tap != tg.tap || ogi != tg.og) {
+                        flush_off();
+                        load_point<DIM>(g, pi, P.offset, tap, ogi, tg);
+                    }
+                    if (tap != tg.mtap || mgi != tg.mg) {
+                        flush_mask();
+                        load_mask<DIM>(g, pi, P.mask, tap, mgi, tg);
+                    }
+                    bool okc[NC];
+                    float wc[NC];
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        int rowi;
+                        corner_of<DIM>(g, pi, tg, deformable, c, okc[c], rowi, wc[c]);
+                        rs[lane * NC + c] = (uint32_t)rowi * (uint32_t)g.Cs;
+                    }
+                    __syncwarp();
+                    const int buf = k % P.g_bufs;
+                    const float *gs = stage_g + (pair * P.g_bufs + buf) * 1024;
+                    // corner loads do not depend on the staged tile: issue them before waiting for it
                     constexpr int ITB = SPLIT ? 2 : 4;
+                    CornerLoad<8, TI> cl[ITB][NC];
+#pragma unroll
+                    for (int i = 0; i < ITB; ++i) {
+#pragma unroll
+                        for (int c = 0; c < NC; ++c)
+                            cl[i][c].load(img + rs[(i * 8 + p8) * NC + c] + (uint32_t)(ch0 + q4 * 8));
+                    }
+                    ok = ptx::mbar_wait(&g_full[pair * 2 + buf], (uint32_t)((k / P.g_bufs) & 1));
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) {
+                        if (lane == 0) atomicExch(P.status, 307);
+                        break;
+                    }
 #pragma unroll
                     for (int it0 = 0; it0 < 4; it0 += ITB) {
-                        CornerLoad<8, TI> cl[ITB][NC];
+                        if (it0 > 0) {
 #pragma unroll
-                        for (int i = 0; i < ITB; ++i) {
-                            const int pos = (it0 + i) * 8 + p8;
+                            for (int i = 0; i < ITB; ++i) {
 #pragma unroll
-                            for (int c = 0; c < NC; ++c)
-                                cl[i][c].load(img + cs[pos * NC + c].off + (uint32_t)(ch0 + q4 * 8));
+                                for (int c = 0; c < NC; ++c)
+                                    cl[i][c].load(img + rs[((it0 + i) * 8 + p8) * NC + c] + (uint32_t)(ch0 + q4 * 8));
+                            }
                         }
 #pragma unroll
                         for (int i = 0; i < ITB; ++i) {
@@ -353,30 +461,15 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                             }
                         }
                     }
-                }
-                if (P.img_grad_cl != nullptr) {
-                    const int quad = lane & 7;
-                    float *dst0 = P.img_grad_cl + ch0 + quad * 4;
-#pragma unroll 2
-                    for (int it = 0; it < 8; ++it) {
-                        const int pos = it * 4 + (lane >> 3);
-                        const float4 qv = *reinterpret_cast<const float4 *>(gs + pos * 32 + ((quad ^ (pos & 7)) << 2));
-#pragma unroll
-                        for (int c = 0; c < NC; ++c) {
-                            const ScatterInfo si = cs[pos * NC + c];
-                            red_add_v4_if(si.scale != 0.f, dst0 + si.off, qv.x * si.scale, qv.y * si.scale, qv.z * si.scale,
-                                          qv.w * si.scale);
-                        }
-                    }
-                }
-                if (want_coord) {
                     __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&g_empty[pair * 2 + buf]);  // staged tile no longer needed
+                    float s_val = 0.f;
                     float dotc[NC];
 #pragma unroll
-                    for (int c = 0; c < NC; ++c) dotc[c] = ds_[lane * NC + c];
-                    float s_val = 0.f;
-#pragma unroll
-                    for (int c = 0; c < NC; ++c) s_val = fmaf(wc[c], dotc[c], s_val);
+                    for (int c = 0; c < NC; ++c) {
+                        dotc[c] = ds_[lane * NC + c];
+                        s_val = fmaf(wc[c], dotc[c], s_val);
+                    }
                     gm_sum += s_val;
                     if (P.goff != nullptr) {
 #pragma unroll
@@ -388,23 +481,19 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                                     float w = ((c >> (DIM - 1 - a)) & 1) ? 1.f : -1.f;
 #pragma unroll
                                     for (int a2 = 0; a2 < DIM; ++a2)
-                                        if (a2 != a) w *= ((c >> (DIM - 1 - a2)) & 1) ? fr[a2] : (1.f - fr[a2]);
+                                        if (a2 != a) w *= ((c >> (DIM - 1 - a2)) & 1) ? tg.fr[a2] : (1.f - tg.fr[a2]);
                                     ds = fmaf(w, dotc[c], ds);
                                 }
                             }
-                            go_sum[a] = fmaf(mval, ds, go_sum[a]);
+                            go_sum[a] = fmaf(tg.mval, ds, go_sum[a]);
                         }
                     }
                 }
             }
-            // release the accumulator
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&t_empty[q]);
+            flush_off();
+            flush_mask();
         }
-        flush_off();
-        flush_mask();
-    } else if (warp == DG_EPI_WARPS) {
+    } else if (warp == DG_MMA_WARP) {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
             const uint32_t idesc = ptx::instr_desc_f16(MODE == TC_F16 ? 0 : 1, TILE_POS, ncol, 0, 0);
@@ -449,7 +538,7 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
             }
         }
         __syncwarp();
-    } else {
+    } else if (warp == DG_TMA_WARP) {
         // ------------------------------------------------------------------ TMA: dense tiles once, weight ring
         if (lane == 0) {
             ptx::mbar_arrive_expect_tx(a_full, a_bytes);
@@ -489,7 +578,7 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
 
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == DG_EPI_WARPS) ptx::tmem_dealloc(tmem_base, DG_TMEM_COLS);
+    if (warp == DG_MMA_WARP) ptx::tmem_dealloc(tmem_base, DG_TMEM_COLS);
 }
 
 // [B, C, S] f32 -> [B, S, C] bf16 hi + lo
@@ -548,16 +637,17 @@ __global__ void __launch_bounds__(256) from_channels_last_bias_kernel(const floa
     }
 }
 
-size_t dgrad_smem_bytes(int mode, int rc, int nb, int b_stages) {
+size_t dgrad_smem_bytes(int dim, int mode, int rc, int nb, int b_stages, int g_bufs) {
     const int parts = mode == TC_SPLIT ? 2 : 1;
-    const size_t staging = (size_t)DG_EPI_WARPS * (32 * 32 * 4 + 32 * 8 * 8 + 32 * 8 * 4);  // epilogue transposition buffers
-    return 1024 + (size_t)rc * parts * DG_A_TILE + (size_t)b_stages * parts * nb * 64 * 128 + (1 + 2 * b_stages + 16) * 8 +
-           48 + staging;
+    const int nc = 1 << dim;
+    const size_t staging = (size_t)DG_PAIRS * (g_bufs * 4096 + 32 * nc * (8 + 4 + 4));  // epilogue buffers
+    return 1024 + (size_t)rc * parts * DG_A_TILE + (size_t)b_stages * parts * nb * 64 * 128 + staging +
+           (49 + 2 * b_stages) * 8 + 16;
 }
 
 template <int DIM, int MODE>
 cudaError_t launch_dgrad_t(const DgradParams<DIM> &P, dim3 grid, const CUtensorMap *maps, cudaStream_t stream) {
-    const size_t smem = dgrad_smem_bytes(MODE, P.rc, P.nb, P.b_stages);
+    const size_t smem = dgrad_smem_bytes(DIM, MODE, P.rc, P.nb, P.b_stages, P.g_bufs);
     auto kern = dcn_dgrad_tc_kernel<DIM, MODE>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -568,18 +658,20 @@ cudaError_t launch_dgrad_t(const DgradParams<DIM> &P, dim3 grid, const CUtensorM
 
 }  // namespace
 
-bool dgrad_tc_config(int mode, int cdg, int csg, int *nb, int *b_stages) {
+// Column-block width, weight-ring depth and staging depth that fit shared memory; false when nothing fits.
+bool dgrad_tc_config(int dim, int mode, int cdg, int csg, int *nb, int *b_stages, int *g_bufs) {
     const int rc = cdg / 64;
-    int n = ((csg / 64) % 2 == 0) ? 2 : 1;
-    int s = 0;
-    for (; n >= 1 && s == 0; --n)
-        for (int cand = tuning_int("TVDCN_B200_DG_STAGES", 4); cand >= 2; --cand)
-            if (dgrad_smem_bytes(mode, rc, n, cand) <= 227 * 1024) { s = cand; break; }
-    if (s == 0) return false;
-    ++n;  // undo the loop's last decrement
-    *nb = n;
-    *b_stages = s;
-    return true;
+    const int n_max = ((csg / 64) % 2 == 0) ? 2 : 1;
+    for (int gb = 2; gb >= 1; --gb)
+        for (int n = n_max; n >= 1; --n)
+            for (int cand = tuning_int("TVDCN_B200_DG_STAGES", 4); cand >= 2; --cand)
+                if (dgrad_smem_bytes(dim, mode, rc, n, cand, gb) <= 227 * 1024) {
+                    *nb = n;
+                    *b_stages = cand;
+                    *g_bufs = gb;
+                    return true;
+                }
+    return false;
 }
 
 cudaError_t launch_to_channels_last_split(const float *src, void *hi, void *lo, int B, int C, int S,
@@ -613,8 +705,8 @@ cudaError_t launch_gemm_scatter_tc(const GeoHost &h, int mode, const void *dense
                                    const float *mask, float *img_grad_cl, float *goff, float *gmask, int *status,
                                    cudaStream_t stream) {
     const int cdg = h.Cd / h.groups, csg = h.Cs / h.groups;
-    int nb = 0, bs = 0;
-    if (!dgrad_tc_config(mode, cdg, csg, &nb, &bs)) return cudaErrorInvalidConfiguration;
+    int nb = 0, bs = 0, gb = 0;
+    if (!dgrad_tc_config(h.dim, mode, cdg, csg, &nb, &bs, &gb)) return cudaErrorInvalidConfiguration;
     const long long BP = (long long)h.B * h.P;
     CUtensorMap maps[4];
     {
@@ -655,6 +747,7 @@ cudaError_t launch_gemm_scatter_tc(const GeoHost &h, int mode, const void *dense
         P.rc = cdg / 64;
         P.b_stages = bs;
         P.chunks_per_tap = csg / CHUNK_C;
+        P.g_bufs = gb;
         if (mode == TC_BF16) return launch_dgrad_t<DIM, TC_BF16>(P, grid, maps, stream);
         if (mode == TC_F16) return launch_dgrad_t<DIM, TC_F16>(P, grid, maps, stream);
         return launch_dgrad_t<DIM, TC_SPLIT>(P, grid, maps, stream);
