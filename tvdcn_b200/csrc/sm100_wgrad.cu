@@ -14,7 +14,9 @@
 //       swizzled row = position layout as the forward kernel and consumed as an MN-major operand.
 // Position ranges are split over CTAs; partial results are added to gw (f32) with atomics.
 //
-// Warp roles (320 threads): warps 0-7 producers + epilogue, warp 8 MMA issue + TMEM owner, warp 9 TMA.
+// Warp roles (704 threads): warps 0-15 producers + epilogue, in two groups that take alternate stages so that
+// one group's gathers are in flight while the other blends and stores; warp 16 MMA issue + TMEM owner;
+// warp 17 TMA; warps 18-21 planners, which run ahead and turn coordinates into plan entries.
 #include <algorithm>
 #include <type_traits>
 
@@ -42,9 +44,15 @@ struct WgradParams {
 
 namespace {
 
-constexpr int WG_PRODUCER_WARPS = 8;
+constexpr int WG_PRODUCER_WARPS = 16;
 constexpr int WG_PRODUCERS = WG_PRODUCER_WARPS * 32;
-constexpr int WG_THREADS = WG_PRODUCERS + 64;
+constexpr int WG_GROUPS = 2;                     // producer groups; group q samples stages i with i % 2 == q
+constexpr int WG_GROUP_WARPS = WG_PRODUCER_WARPS / WG_GROUPS;
+constexpr int WG_GROUP_THREADS = WG_GROUP_WARPS * 32;
+constexpr int WG_PLANNER_WARPS = 4;
+constexpr int WG_PLANNERS = WG_PLANNER_WARPS * 32;
+constexpr int WG_PLAN_BUFS = 3;
+constexpr int WG_THREADS = WG_PRODUCERS + 64 + WG_PLANNERS;
 constexpr int WG_POS = 64;                       // positions per stage
 constexpr int WG_A_TILE = 128 * 128;             // [128 d][64 pos] 16-bit
 constexpr int WG_B_TILE = WG_POS * 128;          // [64 pos][64 ch] 16-bit
@@ -68,13 +76,16 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
     const uint32_t b_stage_bytes = b_part_bytes * PARTS;
     uint8_t *sA = smem;
     uint8_t *sB = sA + (size_t)S * a_stage_bytes;
-    PlanEntry *plan = reinterpret_cast<PlanEntry *>(sB + (size_t)S * b_stage_bytes);   // [2][NS * 64][NC]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(plan + 2 * NS * NC * WG_POS);
+    PlanEntry *plan = reinterpret_cast<PlanEntry *>(sB + (size_t)S * b_stage_bytes);   // [bufs][NS * 64][NC]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(plan + WG_PLAN_BUFS * NS * NC * WG_POS);
     uint64_t *full_s = bars;           // sampled tiles written
     uint64_t *full_d = bars + S;       // dense tiles landed
     uint64_t *empty = bars + 2 * S;
     uint64_t *accum = bars + 3 * S;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * S + 1);
+    uint64_t *plan_full = bars + 3 * S + 1;
+    uint64_t *plan_empty = plan_full + WG_PLAN_BUFS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(plan_empty + WG_PLAN_BUFS);
+    __shared__ uint32_t chan16_s[4];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub_total = g.K * P.chunks_per_tap;                 // 64-column blocks per group
@@ -88,16 +99,28 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
     const uint32_t cols_used = (uint32_t)(MT * NS * 64);
     uint32_t ncols = 32;
     while (ncols < cols_used) ncols <<= 1;
+    constexpr uint32_t ESZ = SPLIT ? 4 : 2;
+    // column blocks are ordered channel chunk outermost, tap innermost: the blocks of one CTA share an
+    // image slab, which stays in L1
+    auto sub_chan0 = [&](int sub) {
+        const int kt = kt0 + sub;
+        return grp * g.csg + (kt < sub_total ? kt / g.K : 0) * CHUNK_C;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            ptx::mbar_init(&full_s[s], WG_PRODUCER_WARPS);
+            ptx::mbar_init(&full_s[s], WG_GROUP_WARPS);
             ptx::mbar_init(&full_d[s], 1);
             ptx::mbar_init(&empty[s], 1);
         }
         ptx::mbar_init(accum, 1);
+        for (int b = 0; b < WG_PLAN_BUFS; ++b) {
+            ptx::mbar_init(&plan_full[b], WG_PLANNER_WARPS);
+            ptx::mbar_init(&plan_empty[b], WG_GROUP_WARPS);
+        }
         ptx::fence_mbar_init();
     }
+    if (threadIdx.x < 4) chan16_s[threadIdx.x] = (uint32_t)sub_chan0(min((int)threadIdx.x, NS - 1)) * ESZ / 16u;
     if (warp == WG_PRODUCER_WARPS + 1 && lane == 0) {
         ptx::prefetch_tmap(&tmap_hi);
         if (SPLIT) ptx::prefetch_tmap(&tmap_lo);
@@ -113,65 +136,31 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
 
     if (warp < WG_PRODUCER_WARPS) {
         // ------------------------------------------------------------------ producers
-        const int t = threadIdx.x;
-        const int my_sub = t / WG_POS, my_slot = t % WG_POS;     // plan entry this thread fills
-        const int my_kt = kt0 + my_sub;
-        const bool my_sub_ok = my_sub < NS && my_kt < sub_total;
-        // column blocks are ordered channel chunk outermost, tap innermost: the blocks of one CTA share an
-        // image slab, which stays in L1
-        const int my_tap = my_sub_ok ? my_kt % g.K : 0;
-        const int my_chan0 = grp * g.csg + (my_sub_ok ? my_kt / g.K : 0) * CHUNK_C;
-        const int my_og = g.og > 0 ? my_chan0 / g.cs_per_og : 0;
-        const int my_mg = g.mg > 0 ? my_chan0 / g.cs_per_mg : 0;
-        const bool deformable = P.offset != nullptr;
-        constexpr uint32_t ESZ = SPLIT ? 4 : 2;
-        const uint32_t row_scale = (uint32_t)g.Cs * ESZ / 16u;
+        const int pgroup = warp / WG_GROUP_WARPS;
+        const int tg = threadIdx.x % WG_GROUP_THREADS;
         const uint4 *img16 = reinterpret_cast<const uint4 *>(P.img_cl);
-        __shared__ uint32_t chan16_s[4];
-        if (my_slot == 0 && my_sub < NS) chan16_s[my_sub] = (uint32_t)my_chan0 * ESZ / 16u;
-        // position of this thread's plan entry in stage i
-        auto position_of = [&](int i) {
-            PosInfo<DIM> pi;
-            const int pc = chunk_begin + i;
-            const int p = (pc % P.chunks_per_image) * WG_POS + my_slot;
-            pi.valid = my_sub_ok && i < n_stages && p < g.P;
-            pi.b = pc / P.chunks_per_image;
-            pi.p = pi.valid ? p : 0;
-            decode_in_image<DIM>(g, pi);
-            return pi;
-        };
-        PosInfo<DIM> pi = position_of(0);
-        if (my_sub < NS) {
-            const RawCoords<DIM> rc0 = load_coords<DIM>(g, pi, P.offset, P.mask, my_tap, my_og, my_mg);
-            build_plan<DIM, MODE>(g, pi, rc0, deformable, my_tap, row_scale, plan + (my_sub * WG_POS + my_slot) * NC);
-        }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
         bool ok = true;
-        for (int i = 0; i < n_stages; ++i) {
+        for (int i = pgroup; i < n_stages; i += WG_GROUPS) {
             const int s = i % S, r = i / S;
-            const int pb = i & 1;
-            // next stage's coordinates are fetched now, its plan is written after this stage's sampling
-            RawCoords<DIM> rcn;
-            PosInfo<DIM> pin = position_of(i + 1);
-            if (my_sub < NS && i + 1 < n_stages) rcn = load_coords<DIM>(g, pin, P.offset, P.mask, my_tap, my_og, my_mg);
+            const int pb = i % WG_PLAN_BUFS;
+            if (ok && !ptx::mbar_wait(&plan_full[pb], (uint32_t)((i / WG_PLAN_BUFS) & 1))) {
+                atomicExch(P.status, 205);
+                ok = false;
+            }
             if (ok && !ptx::mbar_wait(&empty[s], (uint32_t)((r & 1) ^ 1))) {
                 atomicExch(P.status, 201);
                 ok = false;
             }
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                uint8_t *b_hi = sB + (size_t)s * b_stage_bytes;
-                produce_tiles<NC, MODE, WG_PRODUCERS>(b_hi, b_hi + b_part_bytes, WG_B_TILE, WG_POS, NS * WG_POS, img16,
-                                                      chan16_s, plan + pb * NS * WG_POS * NC, t);
-                ptx::fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&full_s[s]);
-            }
-            if (i + 1 < n_stages) {
-                if (my_sub < NS)
-                    build_plan<DIM, MODE>(g, pin, rcn, deformable, my_tap, row_scale,
-                                          plan + (((pb ^ 1) * NS + my_sub) * WG_POS + my_slot) * NC);
-                asm volatile("bar.sync 1, 256;" ::: "memory");
+            ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the __syncwarp below
+            if (!ok) break;
+            uint8_t *b_hi = sB + (size_t)s * b_stage_bytes;
+            produce_tiles<NC, MODE, WG_GROUP_THREADS>(b_hi, b_hi + b_part_bytes, WG_B_TILE, WG_POS, NS * WG_POS, img16,
+                                                      chan16_s, plan + pb * NS * WG_POS * NC, tg);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::mbar_arrive(&full_s[s]);
+                ptx::mbar_arrive(&plan_empty[pb]);
             }
         }
 
@@ -181,13 +170,13 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
                 atomicExch(P.status, 202);
                 ok = false;
             }
-            ok = __all_sync(0xffffffffu, ok);
+            ok = __all_sync(0xffffffffu, ok);  // tcgen05.ld is a whole-warp instruction
             ptx::tc_fence_after();
             if (ok) {
                 const int lane_q = warp & 3;
                 const uint32_t lane_base = tmem_base + ((uint32_t)(lane_q * 32) << 16);
                 const int blocks = MT * NS * 2;  // 32-column blocks
-                for (int cb = (warp >> 2); cb < blocks; cb += 2) {
+                for (int cb = (warp >> 2); cb < blocks; cb += WG_PRODUCER_WARPS / 4) {
                     uint32_t v[32];
                     ptx::tmem_ld_32x32(lane_base + (uint32_t)(cb * 32), v);
                     ptx::tmem_ld_wait();
@@ -243,7 +232,7 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
             if (ok && n_stages > 0) ptx::mma_commit(accum);
         }
         __syncwarp();
-    } else {
+    } else if (warp == WG_PRODUCER_WARPS + 1) {
         // ------------------------------------------------------------------ TMA: dense tiles
         if (lane == 0) {
             int issued = 0;
@@ -266,12 +255,63 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
                 }
                 issued = i + 1;
             }
+            // never leave with a copy still in flight into this CTA's shared memory
             if (issued > 0) {
                 const int i = issued - 1;
                 ptx::mbar_wait(&full_d[i % S], (uint32_t)((i / S) & 1));
             }
         }
         __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ planners
+        // entry e = (column block e / 64, position slot e % 64) of a stage; each thread fills up to two entries
+        constexpr int EPT = 4 * WG_POS / WG_PLANNERS;
+        const int t = threadIdx.x - (WG_PRODUCERS + 64);
+        const bool deformable = P.offset != nullptr;
+        const uint32_t row_scale = (uint32_t)g.Cs * ESZ / 16u;
+        int e_tap[EPT], e_og[EPT], e_mg[EPT];
+        bool e_on[EPT], e_ok[EPT];
+#pragma unroll
+        for (int k = 0; k < EPT; ++k) {
+            const int sub = (t + k * WG_PLANNERS) / WG_POS;
+            const int kt = kt0 + sub;
+            e_on[k] = sub < NS;
+            e_ok[k] = e_on[k] && kt < sub_total;
+            e_tap[k] = e_ok[k] ? kt % g.K : 0;
+            const int chan0 = sub_chan0(sub);
+            e_og[k] = g.og > 0 ? chan0 / g.cs_per_og : 0;
+            e_mg[k] = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
+        }
+        const int slot = t % WG_POS;
+        for (int i = 0; i < n_stages; ++i) {
+            const int pb = i % WG_PLAN_BUFS;
+            const int pc = chunk_begin + i;
+            const int p = (pc % P.chunks_per_image) * WG_POS + slot;
+            PosInfo<DIM> pi[EPT];
+            RawCoords<DIM> rc[EPT];
+#pragma unroll
+            for (int k = 0; k < EPT; ++k) {
+                pi[k].valid = e_ok[k] && p < g.P;
+                pi[k].b = pc / P.chunks_per_image;
+                pi[k].p = pi[k].valid ? p : 0;
+                decode_in_image<DIM>(g, pi[k]);
+                if (e_on[k]) rc[k] = load_coords<DIM>(g, pi[k], P.offset, P.mask, e_tap[k], e_og[k], e_mg[k]);
+            }
+            bool ok = ptx::mbar_wait(&plan_empty[pb], (uint32_t)(((i / WG_PLAN_BUFS) & 1) ^ 1));
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                if (lane == 0) atomicExch(P.status, 206);
+                break;
+            }
+#pragma unroll
+            for (int k = 0; k < EPT; ++k) {
+                if (e_on[k])
+                    build_plan<DIM, MODE>(g, pi[k], rc[k], deformable, e_tap[k], row_scale,
+                                          plan + ((pb * NS) * WG_POS + t + k * WG_PLANNERS) * NC);
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&plan_full[pb]);
+        }
     }
 
     ptx::tc_fence_before();
@@ -282,8 +322,8 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
 size_t wgrad_smem_bytes(int dim, int mode, int n_sub, int m_tiles, int stages) {
     const int parts = mode == TC_SPLIT ? 2 : 1;
     const size_t stage = (size_t)parts * (m_tiles * WG_A_TILE + n_sub * WG_B_TILE);
-    const size_t plan = (size_t)2 * n_sub * (1 << dim) * WG_POS * 8;
-    return 1024 + stages * stage + plan + (3 * stages + 1) * 8 + 16;
+    const size_t plan = (size_t)WG_PLAN_BUFS * n_sub * (1 << dim) * WG_POS * 8;
+    return 1024 + stages * stage + plan + (3 * stages + 1 + 2 * WG_PLAN_BUFS) * 8 + 16;
 }
 
 template <int DIM, int MODE>
@@ -307,7 +347,7 @@ bool wgrad_tc_config(int dim, int mode, int cdg, int P, int *n_sub, int *m_tiles
     int ns = mode == TC_SPLIT ? 2 : 4;
     if (dim == 3 && mode != TC_SPLIT) ns = 4;
     int s = 0;
-    for (int cand = tuning_int("TVDCN_B200_WG_STAGES", 2); cand >= 2; --cand)
+    for (int cand = tuning_int("TVDCN_B200_WG_STAGES", 3); cand >= 2; --cand)
         if (wgrad_smem_bytes(dim, mode, ns, mt, cand) <= 227 * 1024) { s = cand; break; }
     if (s == 0) return false;
     *n_sub = ns;
