@@ -330,6 +330,81 @@ __global__ void __launch_bounds__(256) to_channels_last_kernel(const ET *__restr
     }
 }
 
+// 16-bit [B, C, S] -> [B, S, C] with 16-byte loads, for S and C multiples of 8 and 2.  A 64 x 64 tile is held
+// as 32-bit words of two neighbouring positions; words of a channel pair sit 32 words apart and pairs 65 words
+// apart, so the transposing reads (one channel pair per lane) and the writes are free of bank conflicts.
+__global__ void __launch_bounds__(256) to_channels_last16_kernel(const uint16_t *__restrict__ src,
+                                                                 uint16_t *__restrict__ dst, int C, int S) {
+    __shared__ uint32_t tile[32 * 65];
+    const int b = blockIdx.z;
+    const int s0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
+    const uint16_t *in = src + (int64_t)b * C * S;
+    uint32_t *out = reinterpret_cast<uint32_t *>(dst + (int64_t)b * C * S);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int v = lane & 7;                  // 8 positions s0 + 8 v ...
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+        const int cl = warp * 8 + (lane >> 3) * 2 + pass;   // one parity per instruction
+        const int c = c0 + cl, s = s0 + v * 8;
+        uint4 x = make_uint4(0u, 0u, 0u, 0u);
+        if (c < C && s < S) x = __ldg(reinterpret_cast<const uint4 *>(in + (int64_t)c * S + s));
+        uint32_t *w = tile + (cl >> 1) * 65 + (cl & 1) * 32 + v * 4;
+        w[0] = x.x;
+        w[1] = x.y;
+        w[2] = x.z;
+        w[3] = x.w;
+    }
+    __syncthreads();
+    const int c = c0 + 2 * lane;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int s2 = warp * 4 + i;
+        const uint32_t a = tile[lane * 65 + s2], bb = tile[lane * 65 + 32 + s2];
+        const int s = s0 + 2 * s2;
+        if (c < C && s < S) {
+            out[((int64_t)s * C + c) >> 1] = __byte_perm(a, bb, 0x5410);
+            out[((int64_t)(s + 1) * C + c) >> 1] = __byte_perm(a, bb, 0x7632);
+        }
+    }
+}
+
+// 32-bit [B, C, S] -> [B, S, C] with 16-byte loads and stores, for S and C multiples of 4; 64 x 64 tiles.
+__global__ void __launch_bounds__(256) to_channels_last32_kernel(const uint32_t *__restrict__ src,
+                                                                 uint32_t *__restrict__ dst, int C, int S) {
+    __shared__ uint32_t tile[64 * 65];
+    const int b = blockIdx.z;
+    const int s0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
+    const uint32_t *in = src + (int64_t)b * C * S;
+    uint32_t *out = dst + (int64_t)b * C * S;
+    const int v = threadIdx.x & 15, r = threadIdx.x >> 4;   // 16 vectors per row, 16 rows per pass
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int cl = pass * 16 + r;
+        const int c = c0 + cl, s = s0 + v * 4;
+        uint4 x = make_uint4(0u, 0u, 0u, 0u);
+        if (c < C && s < S) x = __ldg(reinterpret_cast<const uint4 *>(in + (int64_t)c * S + s));
+        uint32_t *w = tile + cl * 65 + v * 4;
+        w[0] = x.x;
+        w[1] = x.y;
+        w[2] = x.z;
+        w[3] = x.w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int sl = pass * 16 + r;
+        const int s = s0 + sl, c = c0 + v * 4;
+        if (c < C && s < S) {
+            uint4 x;
+            x.x = tile[(v * 4 + 0) * 65 + sl];
+            x.y = tile[(v * 4 + 1) * 65 + sl];
+            x.z = tile[(v * 4 + 2) * 65 + sl];
+            x.w = tile[(v * 4 + 3) * 65 + sl];
+            *reinterpret_cast<uint4 *>(out + (int64_t)s * C + c) = x;
+        }
+    }
+}
+
 // [B, S, C] f32 -> [B, C, S] in the destination type.
 template <typename TO>
 __global__ void __launch_bounds__(256) from_channels_last_kernel(const float *__restrict__ src, TO *__restrict__ dst,
@@ -438,9 +513,17 @@ cudaError_t launch_to_channels_last(const void *src, void *dst, int B, int C, in
                                     cudaStream_t stream) {
     dim3 grid((S + 31) / 32, (C + 31) / 32, B);
     LaunchScope scope("to_channels_last", stream);
-    if (elem_bytes == 2)
+    if (elem_bytes == 2 && S % 8 == 0 && C % 2 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(dst) & 3) == 0) {
+        dim3 grid64((S + 63) / 64, (C + 63) / 64, B);
+        to_channels_last16_kernel<<<grid64, 256, 0, stream>>>((const uint16_t *)src, (uint16_t *)dst, C, S);
+    } else if (elem_bytes == 2)
         to_channels_last_kernel<uint16_t><<<grid, 256, 0, stream>>>((const uint16_t *)src, (uint16_t *)dst, C, S);
-    else if (elem_bytes == 4)
+    else if (elem_bytes == 4 && S % 4 == 0 && C % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+             (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        dim3 grid64((S + 63) / 64, (C + 63) / 64, B);
+        to_channels_last32_kernel<<<grid64, 256, 0, stream>>>((const uint32_t *)src, (uint32_t *)dst, C, S);
+    } else if (elem_bytes == 4)
         to_channels_last_kernel<uint32_t><<<grid, 256, 0, stream>>>((const uint32_t *)src, (uint32_t *)dst, C, S);
     else
         return cudaErrorInvalidValue;
