@@ -10,8 +10,8 @@ Rank 0 prints ONE JSON line.  Keys beyond the usual ones:
   value        images/s with every input already resident in HBM, all ranks together (weak scaling: each
                rank owns a full per-GPU batch; the only exchange is the all-reduce of [grad_weight|grad_bias])
   e2e          the same metric through the public operators (tvdcn_b200.ops.*, autograd) with HOST buffers:
-               pinned host -> device copies of the step's inputs and device -> host copies of its results
-               are inside the timed region
+               pinned host -> device copies of every step's inputs and device -> host copies of its results
+               are inside the timed region, on copy streams beside the compute stream (prefetching loader)
   roofline     dominant kernel: algorithmic FLOPs (or bytes) per launch / CUDA-event time per launch, against
                the measured peak in MEASURED_PEAKS.json (fallback figures if the file is absent)
   cpu_baseline the reference's own CPU implementation (oracle/_ref) timed on this box's host cores on a
@@ -363,25 +363,69 @@ class DeviceStep:
 
 
 class HostStep:
-    """The step a user of the public API runs when the data lives in host memory."""
+    """The step a user of the public API runs when the data lives in host memory.
+
+    Three streams, as a training loop with a prefetching loader runs it: a copy-in stream brings step i+1's
+    inputs from pinned host memory into the second of two device buffer sets while the compute stream runs
+    step i through the public operators, and a copy-out stream writes step i-1's results (output, all
+    gradients) to pinned host memory.  Every step's inputs and results cross PCIe inside the timed region;
+    `finish()` makes the compute stream wait for the last copy-out so that the closing event covers it.
+    """
+    NAMES = ('x', 'off', 'm', 'go')
 
     def __init__(self, cfg: Config, ts_pinned, mode: str, device, bucket):
         import tvdcn_b200
         self.ops = tvdcn_b200.ops
-        self.cfg, self.ts, self.mode, self.device, self.bucket = cfg, ts_pinned, mode, device, bucket
+        self.cfg, self.mode, self.device, self.bucket = cfg, mode, device, bucket
         self.dt = torch.bfloat16 if mode == 'bf16' else torch.float32
+        # host tensors in the data type the operator consumes (bf16 images for the bf16 mode)
+        self.host_in = {}
+        for k in self.NAMES:
+            t = ts_pinned[k]
+            if k in ('x', 'go') and self.dt != t.dtype:
+                t = t.to(self.dt).pin_memory()
+            self.host_in[k] = t
+        self.dev_in = [{k: torch.empty(v.shape, dtype=v.dtype, device=device) for k, v in self.host_in.items()}
+                       for _ in range(2)]
         self.w = ts_pinned['w'].to(device, self.dt).requires_grad_(True)
         self.bias = ts_pinned['bias'].to(device).requires_grad_(True)
-        self.host_out = None
-        self.h2d = sum(ts_pinned[k].numel() * 4 for k in ('x', 'off', 'm', 'go'))
+        self.s_in, self.s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+        self.in_done = [None, None]      # event: inputs of the step that uses buffer set b have landed
+        self.comp_done = [None, None]    # event: the step that used buffer set b has finished
+        self.out_done = [None, None]     # event: results of that step are in host memory
+        self.keep = [None, None]         # device results, alive until their copy-out has been waited for
+        self.host_out = [None, None]
+        self.step = 0
+        self.h2d = sum(v.numel() * v.element_size() for v in self.host_in.values())
         self.d2h = 0
 
+    def _copy_in(self, b):
+        """Queue the host -> device copies into buffer set b (after the step that last read it)."""
+        if self.comp_done[b] is not None:
+            self.s_in.wait_event(self.comp_done[b])
+        with torch.cuda.stream(self.s_in):
+            for k in self.NAMES:
+                self.dev_in[b][k].copy_(self.host_in[k], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.s_in)
+        self.in_done[b] = ev
+
     def __call__(self):
-        cfg, ops, dev = self.cfg, self.ops, self.device
-        x = self.ts['x'].to(dev, non_blocking=True).to(self.dt).requires_grad_(True)
-        off = self.ts['off'].to(dev, non_blocking=True).requires_grad_(True)
-        m = self.ts['m'].to(dev, non_blocking=True).requires_grad_(True)
-        go = self.ts['go'].to(dev, non_blocking=True).to(self.dt)
+        cfg, ops = self.cfg, self.ops
+        cur = torch.cuda.current_stream(self.device)
+        b = self.step & 1
+        if self.in_done[b] is None:
+            self._copy_in(b)                       # first step: nothing was prefetched
+        cur.wait_event(self.in_done[b])
+        self.in_done[b] = None
+        if self.out_done[b] is not None:           # results of step - 2 may be freed only after their copy-out
+            cur.wait_event(self.out_done[b])
+        self.keep[b] = None
+        d = self.dev_in[b]
+        x = d['x'].detach().requires_grad_(True)
+        off = d['off'].detach().requires_grad_(True)
+        m = d['m'].detach().requires_grad_(True)
+        go = d['go']
         mask = getattr(ops, f'mask_softmax{cfg.dim}d')(m, cfg.kernel) if cfg.softmax_mask else m
         self.w.grad = None
         self.bias.grad = None
@@ -395,15 +439,32 @@ class HostStep:
         self.bucket.weight_view.copy_(self.w.grad)
         self.bucket.bias_view.copy_(self.bias.grad)
         self.bucket.all_reduce_async()
-        results = [out.detach(), x.grad, off.grad, m.grad]
-        if self.host_out is None:
-            self.host_out = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in results]
-            self.host_out.append(torch.empty(self.bucket.flat.shape, dtype=self.bucket.flat.dtype, pin_memory=True))
-            self.d2h = sum(h.numel() * h.element_size() for h in self.host_out)
-        for h, r in zip(self.host_out, results):
-            h.copy_(r, non_blocking=True)
         self.bucket.wait()
-        self.host_out[-1].copy_(self.bucket.flat, non_blocking=True)
+        results = [out.detach(), x.grad, off.grad, m.grad, self.bucket.flat.clone()]
+        ev = torch.cuda.Event()
+        ev.record(cur)
+        self.comp_done[b] = ev
+        # next step's inputs into the other buffer set, this step's results out
+        self._copy_in(b ^ 1)
+        if self.host_out[b] is None:
+            self.host_out[b] = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in results]
+            self.d2h = sum(h.numel() * h.element_size() for h in self.host_out[b])
+        self.s_out.wait_event(ev)
+        with torch.cuda.stream(self.s_out):
+            for h, r in zip(self.host_out[b], results):
+                h.copy_(r, non_blocking=True)
+            eo = torch.cuda.Event()
+            eo.record(self.s_out)
+        self.out_done[b] = eo
+        self.keep[b] = results
+        self.step += 1
+
+    def finish(self):
+        """Order the compute stream after every queued copy-out (call before the closing event)."""
+        cur = torch.cuda.current_stream(self.device)
+        for ev in self.out_done:
+            if ev is not None:
+                cur.wait_event(ev)
 
 
 def timed(fn, steps, warmup, barrier):
@@ -415,6 +476,8 @@ def timed(fn, steps, warmup, barrier):
     start.record()
     for _ in range(steps):
         fn()
+    if hasattr(fn, 'finish'):
+        fn.finish()
     stop.record()
     torch.cuda.synchronize()
     barrier()
