@@ -296,9 +296,9 @@ def known_traffic(kernel: str, config: int, mode: str):
     """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
     under profiles/ (config2_bf16_tensor_kernels.md); None where no capture exists."""
     table = {
-        'dcn_fwd_tc/cfg2/bf16': 85.17e6 + 24.37e6,
-        'dcn_dgrad_tc/cfg2/bf16': 271.87e6 + 88.79e6,
-        'dcn_wgrad_tc/cfg2/bf16': 137.68e6 + 3.91e6,
+        'dcn_fwd_tc/cfg2/bf16': 85.20e6 + 22.62e6,
+        'dcn_dgrad_tc/cfg2/bf16': 272.26e6 + 91.69e6,
+        'dcn_wgrad_tc/cfg2/bf16': 137.70e6 + 4.09e6,
     }
     return table.get(f'{kernel}/cfg{config}/{mode}')
 

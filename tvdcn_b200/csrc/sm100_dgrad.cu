@@ -664,7 +664,7 @@ bool dgrad_tc_config(int dim, int mode, int cdg, int csg, int *nb, int *b_stages
     const int n_max = ((csg / 64) % 2 == 0) ? 2 : 1;
     for (int gb = 2; gb >= 1; --gb)
         for (int n = n_max; n >= 1; --n)
-            for (int cand = tuning_int("TVDCN_B200_DG_STAGES", 4); cand >= 2; --cand)
+            for (int cand = tuning_int("TVDCN_B200_DG_STAGES", 3); cand >= 2; --cand)
                 if (dgrad_smem_bytes(dim, mode, rc, n, cand, gb) <= 227 * 1024) {
                     *nb = n;
                     *b_stages = cand;

@@ -600,7 +600,7 @@ bool fwd_tc_config(int dim, int mode, int cdg, int *bn, int *stages) {
         if (cand <= cap && cdg % cand == 0) { n = cand; break; }
     if (n == 0) return false;
     int s = 0;
-    for (int cand = tuning_int("TVDCN_B200_FWD_STAGES", 4); cand >= 2; --cand)
+    for (int cand = tuning_int("TVDCN_B200_FWD_STAGES", 3); cand >= 2; --cand)
         if (fwd_tc_smem_bytes(dim, mode, n, cand) <= 227 * 1024) { s = cand; break; }
     if (s == 0) return false;
     *bn = n;

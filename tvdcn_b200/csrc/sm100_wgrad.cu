@@ -347,7 +347,7 @@ bool wgrad_tc_config(int dim, int mode, int cdg, int P, int *n_sub, int *m_tiles
     int ns = mode == TC_SPLIT ? 2 : 4;
     if (dim == 3 && mode != TC_SPLIT) ns = 4;
     int s = 0;
-    for (int cand = tuning_int("TVDCN_B200_WG_STAGES", 3); cand >= 2; --cand)
+    for (int cand = tuning_int("TVDCN_B200_WG_STAGES", 2); cand >= 2; --cand)
         if (wgrad_smem_bytes(dim, mode, ns, mt, cand) <= 227 * 1024) { s = cand; break; }
     if (s == 0) return false;
     *n_sub = ns;
