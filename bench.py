@@ -246,6 +246,19 @@ def cpu_baseline(cfg: Config, seed: int, budget_s: float = 15.0):
                       f'OpenMP loops on all {os.cpu_count()} cores, scatter loop serial as in the reference'}
 
 
+def reference_cuda_baseline(cfg: Config, ts, device, steps: int = 5, warmup: int = 2):
+    """The reference's CUDA backend (im2col + cuBLAS + atomic col2im, fp32) on the same device-resident step."""
+    from oracle import build_ref
+    if not build_ref.load_cuda():
+        return {'unavailable': 'oracle/_ref/libtvdcn_ref_cuda.so is not built (python oracle/build_ref.py --cuda)'}
+    dts = {k: v.to(device) for k, v in ts.items()}
+    secs = timed(lambda: reference_step(cfg, dts), steps, warmup, lambda: None)
+    batch = dts['x'].shape[0]
+    return {'value': batch * steps / secs, 'unit': 'images/s', 'ms_per_step': secs / steps * 1e3, 'dtype': 'f32',
+            'steps': steps, 'kind': "reference CUDA kernels built from the reference sources for sm_100, "
+                                    "torch's cuBLAS GEMMs, TF32 off"}
+
+
 def run_reference_arm(args, cfg):
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
@@ -495,6 +508,9 @@ def main():
     ap.add_argument('--batch', type=int, default=0, help='per-GPU batch (default: the configuration\'s)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--ref-cuda', action='store_true',
+                    help="also time the reference's own CUDA backend (oracle/_ref/libtvdcn_ref_cuda.so, fp32) on "
+                         'this GPU and report it as "reference_cuda" (1 GPU only)')
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     if args.warmup < 3 and args.impl == 'ours':
@@ -594,6 +610,10 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         base = cpu_baseline(cfg, 1000 + args.config)
 
+    ref_cuda = None
+    if rank == 0 and world == 1 and args.ref_cuda:
+        ref_cuda = reference_cuda_baseline(cfg, ts, device)
+
     if rank == 0:
         flops = 3 * cfg.flops_per_pass(batch) * world
         step_s = secs / args.steps
@@ -612,7 +632,7 @@ def main():
             'tensor_frac_of_peak': flops / step_s / 1e12 / pk['tflops_sustained'] / world,
             'algorithmic_gbs': nbytes / step_s / 1e9,
             'hbm_frac_of_peak': nbytes / step_s / 1e9 / pk['hbm_gbs'] / world,
-            'kernels': kernels, 'roofline': roofline, 'cpu_baseline': base, 'e2e': e2e,
+            'kernels': kernels, 'roofline': roofline, 'cpu_baseline': base, 'reference_cuda': ref_cuda, 'e2e': e2e,
             'gpu_launches': int(launches2 - launches1), 'clocks': clocks.summary(),
         }
         print(json.dumps(line))

@@ -1,6 +1,8 @@
 // Engine choice per GEMM-shaped primitive and workspace layout.
 #include "plan.h"
 
+#include <algorithm>
+
 namespace tvdcn_b200 {
 
 namespace {
@@ -30,6 +32,16 @@ const char *tc_common(const tvdcn_problem *p, const GeoHost &g) {
     return nullptr;
 }
 
+// f32 data on the tensor cores: one accumulator may take about 2400 MMAs before the round-toward-zero error of
+// the f32 accumulation (~2e-8 of the result per MMA) eats half of the 1e-4 budget.  The sample -> GEMM kernel adds
+// 12 MMAs per (tap, 64-channel chunk), spread over min(4, 512 / bn) accumulators.
+bool chain_ok(int mode, const GeoHost &g, int bn) {
+    if (mode != 2) return true;
+    const int nacc = std::min(4, 512 / std::max(bn, 1));
+    const long long chain = (long long)g.K * (g.Cs / g.groups / 64) * 12 / nacc;
+    return chain <= 2400;
+}
+
 // buffers of the GEMM -> scatter kernel
 void take_scatter_buffers(Plan &pl, Bump &b, const tvdcn_problem *p, const GeoHost &g, bool scatter) {
     const size_t nw = (size_t)g.Cd * (g.Cs / g.groups) * g.K;
@@ -56,13 +68,13 @@ Plan plan_forward(const tvdcn_problem *p) {
     const size_t nw = (size_t)g.Cd * (g.Cs / g.groups) * g.K;
     int bn = 0, st = 0, gbufs = 0;
     if (why == nullptr && !p->transposed) {
-        if (fwd_tc_config(g.dim, mode, g.Cd / g.groups, &bn, &st)) {
+        if (fwd_tc_config(g.dim, mode, g.Cd / g.groups, &bn, &st) && chain_ok(mode, g, bn)) {
             pl.tensor = pl.tc_sg = true;
             pl.img_cl = b.take((size_t)g.B * g.S * g.Cs * es);
             pl.w_pack = b.take(nw * 2);
             if (p->dtype == TVDCN_F32) pl.w_pack_lo = b.take(nw * 2);
         } else {
-            why = "no tile configuration fits";
+            why = "no tile configuration fits (or the f32 accumulation chain would be too long)";
         }
     } else if (why == nullptr) {
         if (dgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.Cs / g.groups, &bn, &st, &gbufs)) {
@@ -93,7 +105,8 @@ Plan plan_backward(const tvdcn_problem *p, bool want_input, bool want_weight, bo
     if (why == nullptr) {
         int bn = 0, st = 0, ns = 0, mt = 0, gbufs = 0;
         // transposed backward: grad_input is a sample -> GEMM over grad_output
-        if (p->transposed && want_input && fwd_tc_config(g.dim, mode, g.Cd / g.groups, &bn, &st)) {
+        if (p->transposed && want_input && fwd_tc_config(g.dim, mode, g.Cd / g.groups, &bn, &st) &&
+            chain_ok(mode, g, bn)) {
             pl.tc_sg = true;
             pl.w_pack = b.take(nw * 2);
             if (p->dtype == TVDCN_F32) pl.w_pack_lo = b.take(nw * 2);

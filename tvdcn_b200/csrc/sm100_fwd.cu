@@ -86,7 +86,11 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
     const int n0 = (blockIdx.y % tiles_n) * BN;
     const long long m0 = (long long)blockIdx.x * TILE_POS;
     const int n_chunks = g.K * P.chunks_per_tap;
-    const uint32_t ncols = BN < 32 ? 32 : BN;
+    // f32 data: the tensor core's f32 accumulation rounds toward zero, so the error of one accumulator grows
+    // with the number of MMAs added into it.  Chunks go round-robin into NACC accumulators, which the epilogue
+    // adds (round to nearest); this divides the chain length by NACC.
+    const int NACC = SPLIT ? min(4, 512 / BN) : 1;
+    const uint32_t ncols = (uint32_t)(NACC * BN) < 32u ? 32u : (uint32_t)(NACC * BN);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
@@ -184,6 +188,13 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                 uint32_t v[32];
                 ptx::tmem_ld_32x32(lane_base + (uint32_t)(cb * 32), v);
                 ptx::tmem_ld_wait();
+                for (int a = 1; a < NACC && a < n_chunks; ++a) {
+                    uint32_t u[32];
+                    ptx::tmem_ld_32x32(lane_base + (uint32_t)(a * BN + cb * 32), u);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) + __uint_as_float(u[e]));
+                }
                 if (pi.valid) {
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
@@ -226,12 +237,13 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                 for (int k4 = 0; k4 < 4; ++k4) {
                     const uint64_t a_hi = ptx::smem_desc_sw128(a_addr + k4 * 32, 16, 1024);
                     const uint64_t b_hi = ptx::smem_desc_sw128(b_addr + k4 * 32, 16, 1024);
-                    ptx::mma_f16(tmem_base, a_hi, b_hi, idesc, (j > 0 || k4 > 0) ? 1u : 0u);
+                    const uint32_t d_tmem = tmem_base + (uint32_t)((j % NACC) * BN);
+                    ptx::mma_f16(d_tmem, a_hi, b_hi, idesc, (j >= NACC || k4 > 0) ? 1u : 0u);
                     if constexpr (SPLIT) {
                         const uint64_t a_lo = ptx::smem_desc_sw128(a_addr + A_TILE_BYTES + k4 * 32, 16, 1024);
                         const uint64_t b_lo = ptx::smem_desc_sw128(b_addr + b_part_bytes + k4 * 32, 16, 1024);
-                        ptx::mma_f16(tmem_base, a_lo, b_hi, idesc, 1u);
-                        ptx::mma_f16(tmem_base, a_hi, b_lo, idesc, 1u);
+                        ptx::mma_f16(d_tmem, a_lo, b_hi, idesc, 1u);
+                        ptx::mma_f16(d_tmem, a_hi, b_lo, idesc, 1u);
                     }
                 }
                 ptx::mma_commit(&empty[s]);

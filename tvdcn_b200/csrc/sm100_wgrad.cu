@@ -379,7 +379,18 @@ cudaError_t launch_sample_wgrad_tc(const GeoHost &h, int mode, const void *dense
     const int y_tiles = h.groups * ((cdg + 128 * mt - 1) / (128 * mt));
     const int cpi = (h.P + WG_POS - 1) / WG_POS;
     const int total = h.B * cpi;
-    int splits = std::max(1, 148 / std::max(1, k_tiles * y_tiles));
+    const int per_wave = std::max(1, 148 / std::max(1, k_tiles * y_tiles));
+    int splits = per_wave;
+    if (mode == TC_SPLIT) {
+        // The tensor core's f32 accumulation rounds toward zero, so the error of one accumulator grows linearly
+        // with the number of MMAs added into it (measured: ~4e-8 of the result per MMA).  f32 data promises
+        // 1e-4: keep one CTA's chain at 56 stages (672 MMAs) by using more waves of CTAs; the partial sums
+        // meet in grad_weight through round-to-nearest f32 atomics.
+        const int max_stages = 56;
+        int waves = 1;
+        while ((total + waves * per_wave - 1) / (waves * per_wave) > max_stages) ++waves;
+        splits = waves * per_wave;
+    }
     splits = std::min(splits, total);
     const int per = (total + splits - 1) / splits;
     splits = (total + per - 1) / per;
