@@ -264,7 +264,7 @@ def run_reference_arm(args, cfg):
     if rank != 0:
         return
     if not load_reference():
-        print(json.dumps({'impl': 'reference', 'unavailable': 'oracle/_ref is not built and the reference '
+        emit(json.dumps({'impl': 'reference', 'unavailable': 'oracle/_ref is not built and the reference '
                           'checkout is not present on this machine'}))
         return
     seed = 1000 + args.config
@@ -286,7 +286,7 @@ def run_reference_arm(args, cfg):
         'e2e': {'value': ips, 'unit': 'images/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
     }
-    print(json.dumps(line))
+    emit(json.dumps(line))
 
 
 # ------------------------------------------------------------------------------------------------------
@@ -497,7 +497,29 @@ def timed(fn, steps, warmup, barrier):
     return start.elapsed_time(stop) / 1e3  # seconds for all steps
 
 
+_RESULT_FD = None
+
+
+def claim_stdout():
+    """Keep stdout for the one JSON line: whatever libraries print to file descriptor 1 (NCCL's version banner,
+    for one) goes to stderr from here on."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: str):
+    sys.stdout.flush()
+    if _RESULT_FD is None:
+        print(line, flush=True)
+    else:
+        os.write(_RESULT_FD, (line + '\n').encode())
+
+
 def main():
+    claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=20)
@@ -635,7 +657,7 @@ def main():
             'kernels': kernels, 'roofline': roofline, 'cpu_baseline': base, 'reference_cuda': ref_cuda, 'e2e': e2e,
             'gpu_launches': int(launches2 - launches1), 'clocks': clocks.summary(),
         }
-        print(json.dumps(line))
+        emit(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
 
