@@ -16,6 +16,8 @@ Rank 0 prints ONE JSON line.  Keys beyond the usual ones:
                the measured peak in MEASURED_PEAKS.json (fallback figures if the file is absent)
   cpu_baseline the reference's own CPU implementation (oracle/_ref) timed on this box's host cores on a
                bounded sample of the same workload (rank 0, 1 GPU only)
+  reference_cuda  the reference's own CUDA backend (built from its sources for sm_100 into oracle/_ref) timed on
+               the same GPU on the same device-resident step, fp32 (rank 0, 1 GPU only; a reported baseline)
 
 With --impl reference the whole run is the reference's CPU implementation on a bounded sample per step.
 """
@@ -530,9 +532,9 @@ def main():
     ap.add_argument('--batch', type=int, default=0, help='per-GPU batch (default: the configuration\'s)')
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
-    ap.add_argument('--ref-cuda', action='store_true',
-                    help="also time the reference's own CUDA backend (oracle/_ref/libtvdcn_ref_cuda.so, fp32) on "
-                         'this GPU and report it as "reference_cuda" (1 GPU only)')
+    ap.add_argument('--no-ref-cuda', action='store_true',
+                    help="skip timing the reference's own CUDA backend (oracle/_ref/libtvdcn_ref_cuda.so, fp32) on "
+                         'this GPU, reported as "reference_cuda" (1 GPU only)')
     args = ap.parse_args()
     cfg = CONFIGS[args.config]
     if args.warmup < 3 and args.impl == 'ours':
@@ -633,8 +635,11 @@ def main():
         base = cpu_baseline(cfg, 1000 + args.config)
 
     ref_cuda = None
-    if rank == 0 and world == 1 and args.ref_cuda:
-        ref_cuda = reference_cuda_baseline(cfg, ts, device)
+    if rank == 0 and world == 1 and not args.no_ref_cuda:
+        try:
+            ref_cuda = reference_cuda_baseline(cfg, ts, device)
+        except Exception as e:  # a baseline must never cost the measurement
+            ref_cuda = {'unavailable': f'{type(e).__name__}: {e}'[:200]}
 
     if rank == 0:
         flops = 3 * cfg.flops_per_pass(batch) * world

@@ -1,4 +1,5 @@
 // C ABI (include/tvdcn_b200.h): validation, engine choice, workspace layout, kernel sequencing.
+#include <cstdlib>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -349,6 +350,39 @@ int tvdcn_b200_deform_conv_forward(const tvdcn_problem *p, const void *input, co
     return TVDCN_OK;
 }
 
+// Side stream of the backward pass: the weight-gradient kernel and the bias sum do not depend on the scatter
+// kernel, so they run beside it and fill the SMs that the scatter kernel's last, partial wave of CTAs leaves
+// idle.  One stream and two events per host thread and device, created on first use and kept; fork and join are
+// event waits, so the caller's stream still orders the whole call (and a capture of it picks both streams up).
+// TVDCN_B200_OVERLAP=0 keeps everything on the caller's stream, and so does tvdcn_b200_timing_enable(1).
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    bool tried = false;
+};
+static SideStream *side_stream() {
+    static thread_local SideStream per_device[64];
+    static const bool enabled = [] {
+        const char *v = getenv("TVDCN_B200_OVERLAP");
+        return v == nullptr || v[0] != '0';
+    }();
+    // per-kernel timing wants every kernel alone on the GPU
+    if (!enabled || g_timing.load(std::memory_order_relaxed)) return nullptr;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    SideStream &s = per_device[dev];
+    if (!s.tried) {
+        s.tried = true;
+        if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+            s.stream = nullptr;
+            (void)cudaGetLastError();
+        }
+    }
+    return s.stream != nullptr ? &s : nullptr;
+}
+
 int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_output, const void *input,
                                     const void *weight, const void *offset, const void *mask, void *grad_input,
                                     void *grad_weight, void *grad_offset, void *grad_mask, void *grad_bias,
@@ -398,9 +432,23 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
     if (goff_acc) CUDA_TRY(cudaMemsetAsync(goff_acc, 0, n_off * acs, stream));
     if (gmask_acc) CUDA_TRY(cudaMemsetAsync(gmask_acc, 0, n_mask * acs, stream));
 
+    // fork: weight gradient + bias sum on the side stream when both sides run on the tensor cores
+    SideStream *side = (pl.tc_sw && gw_acc && (pl.tc_gs || pl.tc_sg)) ? side_stream() : nullptr;
+    cudaStream_t wstream = stream;
+    if (side != nullptr) {
+        CUDA_TRY(stage_image(p, g, pl, p->transposed ? grad_output : input, ws, stream));
+        CUDA_TRY(cudaEventRecord(side->fork, stream));
+        CUDA_TRY(cudaStreamWaitEvent(side->stream, side->fork, 0));
+        wstream = side->stream;
+    }
+
     if (!p->transposed) {
         // sampled image = input, dense = grad_output
         void *gi_acc = grad_input ? (pl.img_acc != NO_BUF ? (void *)(ws + pl.img_acc) : grad_input) : nullptr;
+        if (side != nullptr) {
+            CUDA_TRY(run_sample_wgrad_tc(p, g, pl, grad_output, input, offset, mask, gw_acc, ws, wstream));
+            if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cd, g.P, grad_bias, wstream));
+        }
         if (pl.tc_gs) {
             CUDA_TRY(run_gemm_scatter_tc(p, g, pl, grad_output, weight, offset, mask, input, grad_input, nullptr,
                                          goff_acc, gmask_acc, ws, stream));
@@ -411,14 +459,21 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
                 CUDA_TRY(launch_gemm_scatter(g, dt, aux, grad_output, weight, offset, mask, input, gi_acc, goff_acc,
                                              gmask_acc, stream));
         }
-        if (gw_acc && pl.tc_sw)
+        if (side != nullptr) {
+            // already queued beside the scatter kernel
+        } else if (gw_acc && pl.tc_sw)
             CUDA_TRY(run_sample_wgrad_tc(p, g, pl, grad_output, input, offset, mask, gw_acc, ws, stream));
         else if (gw_acc)
             CUDA_TRY(launch_sample_wgrad(g, dt, aux, grad_output, input, offset, mask, gw_acc, stream));
-        if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cd, g.P, grad_bias, stream));
+        if (grad_bias && side == nullptr)
+            CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cd, g.P, grad_bias, stream));
         if (gi_acc && pl.img_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(dt, gi_acc, grad_input, n_img, stream));
     } else {
         // sampled image = grad_output, dense = input
+        if (side != nullptr) {
+            CUDA_TRY(run_sample_wgrad_tc(p, g, pl, input, grad_output, offset, mask, gw_acc, ws, wstream));
+            if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cs, g.S, grad_bias, wstream));
+        }
         if ((goff_acc || gmask_acc) && pl.tc_gs)
             CUDA_TRY(run_gemm_scatter_tc(p, g, pl, input, weight, offset, mask, grad_output, nullptr, nullptr, goff_acc,
                                          gmask_acc, ws, stream));
@@ -429,12 +484,19 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
             CUDA_TRY(run_sample_gemm_tc(p, g, pl, grad_output, weight, offset, mask, nullptr, grad_input, ws, stream));
         else if (grad_input)
             CUDA_TRY(launch_sample_gemm(g, dt, aux, grad_output, weight, offset, mask, nullptr, grad_input, stream));
-        if (gw_acc && pl.tc_sw)
+        if (side != nullptr) {
+            // already queued beside the other kernels
+        } else if (gw_acc && pl.tc_sw)
             CUDA_TRY(run_sample_wgrad_tc(p, g, pl, input, grad_output, offset, mask, gw_acc, ws, stream));
         else if (gw_acc)
             CUDA_TRY(launch_sample_wgrad(g, dt, aux, input, grad_output, offset, mask, gw_acc, stream));
-        if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cs, g.S, grad_bias, stream));
+        if (grad_bias && side == nullptr)
+            CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cs, g.S, grad_bias, stream));
         (void)n_dense;
+    }
+    if (side != nullptr) {  // join
+        CUDA_TRY(cudaEventRecord(side->join, side->stream));
+        CUDA_TRY(cudaStreamWaitEvent(stream, side->join, 0));
     }
     if (gw_acc && pl.gw_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(dt, gw_acc, grad_weight, n_w, stream));
     if (goff_acc && pl.goff_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(aux, goff_acc, grad_offset, n_off, stream));
