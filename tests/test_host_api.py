@@ -75,9 +75,44 @@ def test_module_argument_errors():
     with pytest.raises(ValueError, match='scale'):
         ops.mask_sigmoid(torch.zeros(1), scale=0.)
     m = ops.DeformConvTranspose2d(4, 4, 3, stride=2)
+    geom = (m.stride, m.padding, m.kernel_size, 2, m.dilation)
     with pytest.raises(ValueError, match='output size'):
-        m._output_padding(torch.zeros(1, 4, 5, 5), [20, 20])
-    assert m._output_padding(torch.zeros(1, 4, 5, 5), [12, 11]) == [1, 0]
+        m._output_padding(torch.zeros(1, 4, 5, 5), [20, 20], *geom)
+    assert list(m._output_padding(torch.zeros(1, 4, 5, 5), [12, 11], *geom)) == [1, 0]
+    with pytest.raises(ValueError, match='zeros'):
+        ops.DeformConvTranspose2d(4, 4, 3, padding_mode='reflect')
+
+
+def test_everything_compiles_under_torchscript():
+    """The reference advertises that all of its functions and modules are torch.jit.script-able; so are these.
+    The graphs must call the tvdcn:: operators (checked on the scripted code, nothing runs on a GPU here)."""
+    fns = [ops.deform_conv1d, ops.deform_conv2d, ops.deform_conv3d, ops.deform_conv_transpose1d,
+           ops.deform_conv_transpose2d, ops.deform_conv_transpose3d, ops.mask_softmax1d, ops.mask_softmax2d,
+           ops.mask_softmax3d, ops.mask_sigmoid]
+    for f in fns:
+        torch.jit.script(f)
+    for dim in (1, 2, 3):
+        mods = [
+            getattr(ops, f'DeformConv{dim}d')(4, 8, 3, padding=1),
+            getattr(ops, f'DeformConv{dim}d')(4, 8, 3, padding=1, padding_mode='reflect'),
+            getattr(ops, f'PackedDeformConv{dim}d')(4, 8, 3, modulated=True, mask_activation='softmax'),
+            getattr(ops, f'PackedDeformConv{dim}d')(4, 8, 3, deformable=False, modulated=True),
+            getattr(ops, f'DeformConvTranspose{dim}d')(4, 8, 3, stride=2),
+            getattr(ops, f'PackedDeformConvTranspose{dim}d')(4, 8, 3, stride=2, modulated=True),
+            getattr(ops, f'MaskSoftmax{dim}d')(3),
+        ]
+        for m in mods:
+            scripted = torch.jit.script(m)
+            code = scripted.code
+            if 'Deform' in type(m).__name__:
+                name = 'deform_conv_transpose' if 'Transpose' in type(m).__name__ else 'deform_conv'
+                inlined = str(scripted.inlined_graph)
+                assert f'tvdcn::{name}{dim}d' in inlined, type(m).__name__
+            assert code
+    # a scripted module computes what the eager one does (CPU path of mask_softmax)
+    sm = torch.jit.script(ops.MaskSoftmax2d(3))
+    x = torch.randn(2, 18, 4, 5)
+    assert torch.equal(sm(x), ops.mask_softmax2d(x, (3, 3)))
 
 
 def test_mask_softmax_on_cpu_is_the_reference_definition():

@@ -201,3 +201,21 @@ def test_current_stream_is_used():
     before = torch.ops.tvdcn._launch_count()
     ops.deform_conv2d(x, w, off, mask, bias, case.stride, case.padding, case.dilation)
     assert torch.ops.tvdcn._launch_count() > before
+
+
+@pytest.mark.parametrize('dim', [1, 2, 3])
+def test_scripted_modules_run_like_eager(dim):
+    """torch.jit.script of the packed modules (conv and transposed): same output and gradients as eager."""
+    torch.manual_seed(3)
+    size = (9, 8, 7)[:dim]
+    for name, kw in ((f'PackedDeformConv{dim}d', dict(padding=1)), (f'PackedDeformConvTranspose{dim}d', dict(stride=2))):
+        m = getattr(ops, name)(4, 6, 3, modulated=True, mask_activation='softmax', offset_groups=2, **kw).cuda()
+        for gen in (m.offset_generator, m.mask_generator):
+            torch.nn.init.normal_(gen.weight, std=0.3)
+        sm = torch.jit.script(m)
+        x = torch.randn(2, 4, *size, device='cuda', requires_grad=True)
+        y0 = m(x)
+        g0, = torch.autograd.grad(y0.square().sum(), x)
+        y1 = sm(x)
+        g1, = torch.autograd.grad(y1.square().sum(), x)
+        assert nerr(y1, y0) < 1e-6 and nerr(g1, g0) < 1e-5, name

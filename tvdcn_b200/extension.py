@@ -12,7 +12,7 @@ from typing import List
 
 import torch
 
-__all__ = ['has_ops', 'with_cuda', 'cuda_version', 'cuda_arch_list', 'c_abi']
+__all__ = ['has_ops', 'with_cuda', 'cuda_version', 'cuda_arch_list', 'c_abi', 'load_error']
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 _EXT_PATH = os.path.join(_PKG_DIR, '_C.so')
@@ -20,6 +20,12 @@ _LIB_PATH = os.path.join(_PKG_DIR, 'libtvdcn_b200.so')
 
 _HAS_OPS = False
 _LOAD_ERROR = None
+
+
+def _has_ops() -> bool:
+    # replaced by a function that returns True once the extension is loaded; a plain function (not a
+    # module-level flag) so that TorchScript can compile callers of _assert_has_ops()
+    return False
 
 
 def _load() -> None:
@@ -36,12 +42,21 @@ def _load() -> None:
 
 _load()
 
+if _HAS_OPS:
+    def _has_ops() -> bool:  # noqa: F811
+        return True
+
 
 def _assert_has_ops() -> None:
-    if not _HAS_OPS:
+    if not _has_ops():
         raise RuntimeError(
             'tvdcn_b200: the compiled extension is not available and there is no fallback path. '
-            + str(_LOAD_ERROR))
+            'Build it with `python -m tvdcn_b200.build`; tvdcn_b200.extension.load_error() has the detail.')
+
+
+def load_error():
+    """Why the compiled extension could not be loaded (None when it was)."""
+    return _LOAD_ERROR
 
 
 def has_ops() -> bool:

@@ -13,12 +13,13 @@ Layouts (D = 1, 2, 3; taps = prod(kernel_size)):
 ``offset=None`` samples the integer grid, ``mask=None`` multiplies by one; with both absent the operator
 is an ordinary convolution.
 """
-from typing import Callable, Optional, Union
+from typing import Callable, List, Optional, Tuple, Union
 
 import torch
 import torch.nn.functional as F
 from torch import Tensor, nn
 from torch.nn import init
+from torch.nn.common_types import _size_1_t, _size_2_t, _size_3_t
 from torch.nn.modules.conv import _ConvNd
 from torch.nn.modules.utils import _single, _pair, _triple
 
@@ -36,38 +37,55 @@ _MASK_SOFTMAX = {1: MaskSoftmax1d, 2: MaskSoftmax2d, 3: MaskSoftmax3d}
 _CONV = {1: nn.Conv1d, 2: nn.Conv2d, 3: nn.Conv3d}
 
 
-def _ints(v, dim: int):
-    # the dispatcher wants lists for SymInt[D] arguments; ints are broadcast here
-    return [int(e) for e in _NTUPLE[dim](v)]
+# The dispatcher wants a list for every SymInt[D] argument and does not broadcast a bare int; these do it, in
+# eager mode and under TorchScript alike.
+def _list1(v: _size_1_t) -> List[int]:
+    if isinstance(v, int):
+        return [v]
+    return [v[0]]
 
 
-def _deform_conv(dim, input, weight, offset, mask, bias, stride, padding, dilation, groups):
-    _assert_has_ops()
-    op = getattr(torch.ops.tvdcn, f'deform_conv{dim}d')
-    return op(input, weight, offset, mask, bias,
-              _ints(stride, dim), _ints(padding, dim), _ints(dilation, dim), groups)
+def _list2(v: _size_2_t) -> List[int]:
+    if isinstance(v, int):
+        return [v, v]
+    return [v[0], v[1]]
+
+
+def _list3(v: _size_3_t) -> List[int]:
+    if isinstance(v, int):
+        return [v, v, v]
+    return [v[0], v[1], v[2]]
 
 
 def deform_conv1d(input: Tensor, weight: Tensor, offset: Optional[Tensor] = None, mask: Optional[Tensor] = None,
-                  bias: Optional[Tensor] = None, stride=1, padding=0, dilation=1, groups: int = 1) -> Tensor:
+                  bias: Optional[Tensor] = None, stride: _size_1_t = 1, padding: _size_1_t = 0,
+                  dilation: _size_1_t = 1, groups: int = 1) -> Tensor:
     """1D deformable convolution; returns [batch, out_channels, out_width]."""
-    return _deform_conv(1, input, weight, offset, mask, bias, stride, padding, dilation, groups)
+    _assert_has_ops()
+    return torch.ops.tvdcn.deform_conv1d(input, weight, offset, mask, bias, _list1(stride), _list1(padding),
+                                         _list1(dilation), groups)
 
 
 def deform_conv2d(input: Tensor, weight: Tensor, offset: Optional[Tensor] = None, mask: Optional[Tensor] = None,
-                  bias: Optional[Tensor] = None, stride=1, padding=0, dilation=1, groups: int = 1) -> Tensor:
+                  bias: Optional[Tensor] = None, stride: _size_2_t = 1, padding: _size_2_t = 0,
+                  dilation: _size_2_t = 1, groups: int = 1) -> Tensor:
     """2D deformable convolution (DCNv1 / DCNv2); returns [batch, out_channels, out_height, out_width]."""
-    return _deform_conv(2, input, weight, offset, mask, bias, stride, padding, dilation, groups)
+    _assert_has_ops()
+    return torch.ops.tvdcn.deform_conv2d(input, weight, offset, mask, bias, _list2(stride), _list2(padding),
+                                         _list2(dilation), groups)
 
 
 def deform_conv3d(input: Tensor, weight: Tensor, offset: Optional[Tensor] = None, mask: Optional[Tensor] = None,
-                  bias: Optional[Tensor] = None, stride=1, padding=0, dilation=1, groups: int = 1) -> Tensor:
+                  bias: Optional[Tensor] = None, stride: _size_3_t = 1, padding: _size_3_t = 0,
+                  dilation: _size_3_t = 1, groups: int = 1) -> Tensor:
     """3D deformable convolution; returns [batch, out_channels, out_depth, out_height, out_width]."""
-    return _deform_conv(3, input, weight, offset, mask, bias, stride, padding, dilation, groups)
+    _assert_has_ops()
+    return torch.ops.tvdcn.deform_conv3d(input, weight, offset, mask, bias, _list3(stride), _list3(padding),
+                                         _list3(dilation), groups)
 
 
 ################################################################################
-# Modules
+# Modules (all of them compile under torch.jit.script, like the reference's)
 ################################################################################
 def _resolve_mask_activation(mask_activation, dim, kernel_size):
     if isinstance(mask_activation, str):
@@ -81,9 +99,8 @@ def _resolve_mask_activation(mask_activation, dim, kernel_size):
 
 # noinspection PyMethodOverriding
 class _DeformConvNd(_ConvNd):
-    """Shared implementation; subclasses fix ``_dim``."""
+    """Shared constructor; subclasses fix ``_dim`` and the operator call."""
     _dim = 0
-    _transposed = False
 
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1,
                  groups: int = 1, bias: bool = True, padding_mode: str = 'zeros', device=None, dtype=None) -> None:
@@ -94,12 +111,7 @@ class _DeformConvNd(_ConvNd):
 
     def _conv_forward(self, input: Tensor, weight: Tensor, offset: Optional[Tensor], mask: Optional[Tensor],
                       bias: Optional[Tensor]) -> Tensor:
-        if self.padding_mode != 'zeros':
-            padded = F.pad(input, self._reversed_padding_repeated_twice, mode=self.padding_mode)
-            return _deform_conv(self._dim, padded, weight, offset, mask, bias, self.stride,
-                                (0,) * self._dim, self.dilation, self.groups)
-        return _deform_conv(self._dim, input, weight, offset, mask, bias, self.stride, self.padding,
-                            self.dilation, self.groups)
+        raise NotImplementedError
 
     def forward(self, input: Tensor, offset: Optional[Tensor], mask: Optional[Tensor] = None) -> Tensor:
         return self._conv_forward(input, self.weight, offset, mask, self.bias)
@@ -121,15 +133,39 @@ class DeformConv1d(_DeformConvNd):
     """See :func:`deform_conv1d`.  ``forward(input, offset, mask=None)``."""
     _dim = 1
 
+    def _conv_forward(self, input: Tensor, weight: Tensor, offset: Optional[Tensor], mask: Optional[Tensor],
+                      bias: Optional[Tensor]) -> Tensor:
+        if self.padding_mode != 'zeros':
+            return deform_conv1d(F.pad(input, self._reversed_padding_repeated_twice, mode=self.padding_mode),
+                                 weight, offset, mask, bias, self.stride, (0,), self.dilation, self.groups)
+        return deform_conv1d(input, weight, offset, mask, bias, self.stride, self.padding, self.dilation,
+                             self.groups)
+
 
 class DeformConv2d(_DeformConvNd):
     """See :func:`deform_conv2d`.  ``forward(input, offset, mask=None)``."""
     _dim = 2
 
+    def _conv_forward(self, input: Tensor, weight: Tensor, offset: Optional[Tensor], mask: Optional[Tensor],
+                      bias: Optional[Tensor]) -> Tensor:
+        if self.padding_mode != 'zeros':
+            return deform_conv2d(F.pad(input, self._reversed_padding_repeated_twice, mode=self.padding_mode),
+                                 weight, offset, mask, bias, self.stride, (0, 0), self.dilation, self.groups)
+        return deform_conv2d(input, weight, offset, mask, bias, self.stride, self.padding, self.dilation,
+                             self.groups)
+
 
 class DeformConv3d(_DeformConvNd):
     """See :func:`deform_conv3d`.  ``forward(input, offset, mask=None)``."""
     _dim = 3
+
+    def _conv_forward(self, input: Tensor, weight: Tensor, offset: Optional[Tensor], mask: Optional[Tensor],
+                      bias: Optional[Tensor]) -> Tensor:
+        if self.padding_mode != 'zeros':
+            return deform_conv3d(F.pad(input, self._reversed_padding_repeated_twice, mode=self.padding_mode),
+                                 weight, offset, mask, bias, self.stride, (0, 0, 0), self.dilation, self.groups)
+        return deform_conv3d(input, weight, offset, mask, bias, self.stride, self.padding, self.dilation,
+                             self.groups)
 
 
 class _PackedMixin:
@@ -182,49 +218,83 @@ class _PackedMixin:
                 if gen.bias is not None:
                     init.zeros_(gen.bias)
 
-    def _offset_and_mask(self, input: Tensor):
-        offset = mask = None
-        if self.deformable and self.offset_generator is not None:
+    def _offset_and_mask(self, input: Tensor) -> Tuple[Optional[Tensor], Optional[Tensor]]:
+        offset: Optional[Tensor] = None
+        mask: Optional[Tensor] = None
+        if self.offset_generator is not None:
             offset = self.offset_generator(input)
             if self.offset_activation is not None:
                 offset = self.offset_activation(offset)
-        if self.modulated and self.mask_generator is not None:
+        if self.mask_generator is not None:
             mask = self.mask_generator(input)
             if self.mask_activation is not None:
                 mask = self.mask_activation(mask)
         return offset, mask
 
 
+def _packed_init(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, offset_groups,
+                 mask_groups, bias, generator_bias, deformable, modulated, offset_activation, mask_activation,
+                 padding_mode, device, dtype):
+    _DeformConvNd.__init__(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias,
+                           padding_mode, device, dtype)
+    # generators see the same window as the main kernel so offset / mask land on the output grid
+    gen = dict(kernel_size=self.kernel_size, stride=self.stride, padding=self.padding, dilation=self.dilation)
+    self._init_packed(offset_groups, mask_groups, generator_bias, deformable, modulated,
+                      offset_activation, mask_activation, gen, device, dtype)
+
+
 # noinspection PyMethodOverriding
-class _PackedDeformConvNd(_PackedMixin, _DeformConvNd):
+class PackedDeformConv1d(_PackedMixin, DeformConv1d):
+    """:class:`DeformConv1d` that computes its own offset (and mask) from the input."""
+
     def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1,
                  groups: int = 1, offset_groups: int = 1, mask_groups: int = 1, bias: bool = True,
                  generator_bias: bool = False, deformable: bool = True, modulated: bool = False,
                  offset_activation: Optional[Union[str, Callable]] = None,
                  mask_activation: Optional[Union[str, Callable]] = 'sigmoid',
                  padding_mode: str = 'zeros', device=None, dtype=None) -> None:
-        super().__init__(in_channels, out_channels, kernel_size, stride, padding, dilation, groups, bias,
-                         padding_mode, device, dtype)
-        # generators see the same window as the main kernel so offset / mask land on the output grid
-        gen = dict(kernel_size=self.kernel_size, stride=self.stride, padding=self.padding, dilation=self.dilation)
-        self._init_packed(offset_groups, mask_groups, generator_bias, deformable, modulated,
-                          offset_activation, mask_activation, gen, device, dtype)
+        _packed_init(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, offset_groups,
+                     mask_groups, bias, generator_bias, deformable, modulated, offset_activation, mask_activation,
+                     padding_mode, device, dtype)
 
     def forward(self, input: Tensor) -> Tensor:
         offset, mask = self._offset_and_mask(input)
         return self._conv_forward(input, self.weight, offset, mask, self.bias)
 
 
-class PackedDeformConv1d(_PackedDeformConvNd):
-    """:class:`DeformConv1d` that computes its own offset (and mask) from the input."""
-    _dim = 1
-
-
-class PackedDeformConv2d(_PackedDeformConvNd):
+# noinspection PyMethodOverriding
+class PackedDeformConv2d(_PackedMixin, DeformConv2d):
     """:class:`DeformConv2d` that computes its own offset (and mask) from the input."""
-    _dim = 2
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1,
+                 groups: int = 1, offset_groups: int = 1, mask_groups: int = 1, bias: bool = True,
+                 generator_bias: bool = False, deformable: bool = True, modulated: bool = False,
+                 offset_activation: Optional[Union[str, Callable]] = None,
+                 mask_activation: Optional[Union[str, Callable]] = 'sigmoid',
+                 padding_mode: str = 'zeros', device=None, dtype=None) -> None:
+        _packed_init(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, offset_groups,
+                     mask_groups, bias, generator_bias, deformable, modulated, offset_activation, mask_activation,
+                     padding_mode, device, dtype)
+
+    def forward(self, input: Tensor) -> Tensor:
+        offset, mask = self._offset_and_mask(input)
+        return self._conv_forward(input, self.weight, offset, mask, self.bias)
 
 
-class PackedDeformConv3d(_PackedDeformConvNd):
+# noinspection PyMethodOverriding
+class PackedDeformConv3d(_PackedMixin, DeformConv3d):
     """:class:`DeformConv3d` that computes its own offset (and mask) from the input."""
-    _dim = 3
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size, stride=1, padding=0, dilation=1,
+                 groups: int = 1, offset_groups: int = 1, mask_groups: int = 1, bias: bool = True,
+                 generator_bias: bool = False, deformable: bool = True, modulated: bool = False,
+                 offset_activation: Optional[Union[str, Callable]] = None,
+                 mask_activation: Optional[Union[str, Callable]] = 'sigmoid',
+                 padding_mode: str = 'zeros', device=None, dtype=None) -> None:
+        _packed_init(self, in_channels, out_channels, kernel_size, stride, padding, dilation, groups, offset_groups,
+                     mask_groups, bias, generator_bias, deformable, modulated, offset_activation, mask_activation,
+                     padding_mode, device, dtype)
+
+    def forward(self, input: Tensor) -> Tensor:
+        offset, mask = self._offset_and_mask(input)
+        return self._conv_forward(input, self.weight, offset, mask, self.bias)
