@@ -148,6 +148,13 @@ size_t tvdcn_b200_static_scratch_bytes(void);
  *   (tvdcn/csrc/ops/cuda/deform_conv_transpose2d_kernel.cpp:374-636 and its 1d/3d twins).
  * Every non-NULL gradient pointer is fully overwritten (no pre-zeroing needed); a NULL
  * gradient pointer skips that gradient.  grad_bias has out_channels elements.
+ *
+ * Streams: everything is ordered by cuda_stream.  When the tensor-core kernels run, the weight gradient and the
+ * bias sum are queued on a second, library-owned stream that forks from cuda_stream and joins it again before
+ * the call returns (event waits only, nothing blocks the host); work queued on cuda_stream after the call sees
+ * all results.  The library creates that stream and its two events once per host thread and device, on the
+ * first such call (make it outside any stream capture).  TVDCN_B200_OVERLAP=0 in the environment keeps all
+ * kernels on cuda_stream.
  */
 int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p,
                                     const void *grad_output,
