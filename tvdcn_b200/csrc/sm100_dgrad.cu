@@ -245,7 +245,7 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
         }
         for (int i = 0; i < 16; ++i) {
             ptx::mbar_init(&g_full[i], 1);
-            ptx::mbar_init(&g_empty[i], 1);
+            ptx::mbar_init(&g_empty[i], SPLIT ? 1 : 2);   // 16-bit: two coordinate warps read every staged tile
         }
         ptx::fence_mbar_init();
     }
@@ -362,9 +362,175 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
         }
     } else if (warp < 2 * DG_PAIRS) {
         // ------------------------------------------------------------------ coordinate warps
-        // read the tile its scatter warp staged, gather the image corners with 4 lanes per position and
-        // turn <col, corner row> dot products into grad_offset / grad_mask sums
-        if (want_coord) {
+        // Coordinate warp (q, sub) takes 16 of the 32 positions of lane quadrant q, all 64 channels of the chunk:
+        // it reads the two 32-channel tiles that scatter warps q and q + 4 staged, gathers the image corners with
+        // 8 lanes per row (a warp-wide load touches 4 rows of 128 / 256 contiguous bytes) and turns
+        // <col, corner row> dot products into grad_offset / grad_mask sums kept by lanes 0-15 (one position each).
+        if (want_coord && !SPLIT) {
+            const int cw = warp - DG_PAIRS;
+            const int lane_q = cw & 3, sub = cw >> 2;
+            const int own = lane & 15;
+            const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + lane_q * 32 + sub * 16 + own);
+            const bool mine = pi.valid && lane < 16;
+            const TI *img = reinterpret_cast<const TI *>(P.img_cl);
+            TapGeometry<DIM> tg;
+            uint32_t *rs = stage_r + cw * 32 * NC;     // [16][NC] row offsets
+            float *ds_ = stage_d + cw * 32 * NC;       // [16][NC] dot products
+            float go_sum[DIM], gm_sum = 0.f;
+#pragma unroll
+            for (int a = 0; a < DIM; ++a) go_sum[a] = 0.f;
+            auto flush_off = [&]() {
+                if (P.goff != nullptr && tg.tap >= 0 && mine) {
+#pragma unroll
+                    for (int a = 0; a < DIM; ++a)
+                        atomicAdd(P.goff + ((((int64_t)pi.b * g.og + tg.og) * g.K + tg.tap) * DIM + a) * (int64_t)g.P + pi.p,
+                                  go_sum[a]);
+                }
+#pragma unroll
+                for (int a = 0; a < DIM; ++a) go_sum[a] = 0.f;
+            };
+            auto flush_mask = [&]() {
+                if (P.gmask != nullptr && tg.mtap >= 0 && mine)
+                    atomicAdd(P.gmask + (((int64_t)pi.b * g.mg + tg.mg) * g.K + tg.mtap) * (int64_t)g.P + pi.p, gm_sum);
+                gm_sum = 0.f;
+            };
+            const int q8 = lane & 7, p4 = lane >> 3;
+            const int half = q8 >> 2;                 // which scatter warp staged this lane's 8 channels
+            const int sw = lane_q + 4 * half;
+            const int ci0 = 2 * (q8 & 3);             // first of its two 16-byte chunks in that warp's row
+            int k = 0;
+            bool ok = true;
+            for (int blk = 0; blk < n_blocks && ok; ++blk) {
+                const int tap = blk % g.K;
+                const int cc0 = (blk / g.K) * NB;
+                for (int ci = 0; ci < NB; ++ci, ++k) {
+                    const int chan0 = grp * g.csg + (cc0 + ci) * CHUNK_C;
+                    const int ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
+                    const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
+                    if (tap != tg.tap || ogi != tg.og) {
+                        flush_off();
+                        load_point<DIM>(g, pi, P.offset, tap, ogi, tg);
+                    }
+                    if (tap != tg.mtap || mgi != tg.mg) {
+                        flush_mask();
+                        load_mask<DIM>(g, pi, P.mask, tap, mgi, tg);
+                    }
+                    bool okc[NC];
+                    float wc[NC];
+                    __syncwarp();
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        int rowi;
+                        corner_of<DIM>(g, pi, tg, deformable, c, okc[c], rowi, wc[c]);
+                        if (lane < 16) rs[own * NC + c] = (uint32_t)rowi * (uint32_t)g.Cs;
+                    }
+                    __syncwarp();
+                    const int buf = k % P.g_bufs;
+                    const float *gs = stage_g + (sw * P.g_bufs + buf) * 1024;
+                    // 16-bit image: lane q8 owns channels 8 q8 .. 8 q8 + 7 (16 bytes; 8 lanes = one 128-byte row).
+                    // f32 image: lane q8 owns channels 4 q8 .. + 3 and 32 + 4 q8 .. + 3, so that each of its two
+                    // 16-byte loads lines up with its neighbours' into a full 128-byte line.
+                    auto load_corner = [&](CornerLoad<8, TI> &dst, const TI *row) {
+                        if constexpr (SPLIT) {
+                            dst.v[0] = __ldg(reinterpret_cast<const float4 *>(row + q8 * 4));
+                            dst.v[1] = __ldg(reinterpret_cast<const float4 *>(row + 32 + q8 * 4));
+                        } else {
+                            dst.load(row + q8 * 8);
+                        }
+                    };
+                    // corner loads do not depend on the staged tiles: issue them before waiting
+                    constexpr int ITB = SPLIT ? 2 : 4;
+                    CornerLoad<8, TI> cl[ITB][NC];
+#pragma unroll
+                    for (int i = 0; i < ITB; ++i) {
+#pragma unroll
+                        for (int c = 0; c < NC; ++c)
+                            load_corner(cl[i][c], img + rs[(i * 4 + p4) * NC + c] + (uint32_t)chan0);
+                    }
+                    const uint32_t par = (uint32_t)((k / P.g_bufs) & 1);
+                    ok = ptx::mbar_wait(&g_full[lane_q * 2 + buf], par) && ptx::mbar_wait(&g_full[(lane_q + 4) * 2 + buf], par);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) {
+                        if (lane == 0) atomicExch(P.status, 307);
+                        break;
+                    }
+#pragma unroll
+                    for (int it0 = 0; it0 < 4; it0 += ITB) {
+                        if (it0 > 0) {
+#pragma unroll
+                            for (int i = 0; i < ITB; ++i) {
+#pragma unroll
+                                for (int c = 0; c < NC; ++c)
+                                    load_corner(cl[i][c], img + rs[((it0 + i) * 4 + p4) * NC + c] + (uint32_t)chan0);
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < ITB; ++i) {
+                            const int p16 = (it0 + i) * 4 + p4;      // position within this warp's 16
+                            const int row = sub * 16 + p16;          // row of the staged 32-position tiles
+                            float4 g0, g1;
+                            if constexpr (SPLIT) {
+                                // chunk q8 of the lower and of the upper 32 channels
+                                const float *lo = stage_g + (lane_q * P.g_bufs + buf) * 1024 + row * 32;
+                                const float *hi = stage_g + ((lane_q + 4) * P.g_bufs + buf) * 1024 + row * 32;
+                                g0 = *reinterpret_cast<const float4 *>(lo + ((q8 ^ (row & 7)) << 2));
+                                g1 = *reinterpret_cast<const float4 *>(hi + ((q8 ^ (row & 7)) << 2));
+                            } else {
+                                // the two halves read their chunk pair in opposite order: 8 distinct banks per phase
+                                const float4 ga = *reinterpret_cast<const float4 *>(gs + row * 32 + (((ci0 + half) ^ (row & 7)) << 2));
+                                const float4 gb = *reinterpret_cast<const float4 *>(gs + row * 32 + (((ci0 + 1 - half) ^ (row & 7)) << 2));
+                                g0 = half ? gb : ga;
+                                g1 = half ? ga : gb;
+                            }
+                            const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                            for (int c = 0; c < NC; ++c) {
+                                float d = cl[i][c].dot(gg);
+                                d += __shfl_xor_sync(0xffffffffu, d, 1);
+                                d += __shfl_xor_sync(0xffffffffu, d, 2);
+                                d += __shfl_xor_sync(0xffffffffu, d, 4);
+                                if (q8 == 0) ds_[p16 * NC + c] = d;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) {   // both staged tiles are no longer needed by this warp
+                        ptx::mbar_arrive(&g_empty[lane_q * 2 + buf]);
+                        ptx::mbar_arrive(&g_empty[(lane_q + 4) * 2 + buf]);
+                    }
+                    float s_val = 0.f;
+                    float dotc[NC];
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        dotc[c] = ds_[own * NC + c];
+                        s_val = fmaf(wc[c], dotc[c], s_val);
+                    }
+                    gm_sum += s_val;
+                    if (P.goff != nullptr) {
+#pragma unroll
+                        for (int a = 0; a < DIM; ++a) {
+                            float ds = 0.f;
+#pragma unroll
+                            for (int c = 0; c < NC; ++c) {
+                                if (okc[c]) {
+                                    float w = ((c >> (DIM - 1 - a)) & 1) ? 1.f : -1.f;
+#pragma unroll
+                                    for (int a2 = 0; a2 < DIM; ++a2)
+                                        if (a2 != a) w *= ((c >> (DIM - 1 - a2)) & 1) ? tg.fr[a2] : (1.f - tg.fr[a2]);
+                                    ds = fmaf(w, dotc[c], ds);
+                                }
+                            }
+                            go_sum[a] = fmaf(tg.mval, ds, go_sum[a]);
+                        }
+                    }
+                }
+            }
+            flush_off();
+            flush_mask();
+        }
+        if (want_coord && SPLIT) {
+            // f32 image: one coordinate warp per scatter warp, 32 positions x 32 channels, 4 lanes per position
+            // (measured faster than the full-row mapping below for 256-byte rows)
             const int pair = warp - DG_PAIRS;
             const int lane_q = pair & 3, half = pair >> 2;
             const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + lane_q * 32 + lane);
