@@ -827,7 +827,7 @@ cudaError_t launch_dgrad_t(const DgradParams<DIM> &P, dim3 grid, const CUtensorM
 // Column-block width, weight-ring depth and staging depth that fit shared memory; false when nothing fits.
 bool dgrad_tc_config(int dim, int mode, int cdg, int csg, int *nb, int *b_stages, int *g_bufs) {
     const int rc = cdg / 64;
-    const int n_max = ((csg / 64) % 2 == 0) ? 2 : 1;
+    const int n_max = std::min(((csg / 64) % 2 == 0) ? 2 : 1, std::max(1, tuning_int("TVDCN_B200_DG_NB", 2)));
     for (int gb = std::min(2, std::max(1, tuning_int("TVDCN_B200_DG_GBUFS", 2))); gb >= 1; --gb)
         for (int n = n_max; n >= 1; --n)
             for (int cand = tuning_int("TVDCN_B200_DG_STAGES", 3); cand >= 2; --cand)
