@@ -606,15 +606,17 @@ size_t fwd_tc_smem_bytes(int dim, int mode, int bn, int stages) {
 
 // Picks the dense-channel tile and the pipeline depth; returns false when the shape is not covered.
 bool fwd_tc_config(int dim, int mode, int cdg, int *bn, int *stages) {
-    const int cap = mode == TC_SPLIT ? 128 : 256;
-    int n = 0;
-    for (int cand : {256, 128, 64})
-        if (cand <= cap && cdg % cand == 0) { n = cand; break; }
+    const int cap = mode == TC_SPLIT ? tuning_int("TVDCN_B200_FWD_BN_SPLIT", 256) : 256;
+    // widest tile of dense channels first (the sampled tile is produced once per CTA, so a wider tile divides the
+    // sampling work), then the deepest pipeline that fits
+    int n = 0, s = 0;
+    for (int cand_n : {256, 128, 64}) {
+        if (cand_n > cap || cdg % cand_n != 0) continue;
+        for (int cand = tuning_int("TVDCN_B200_FWD_STAGES", 3); cand >= 2; --cand)
+            if (fwd_tc_smem_bytes(dim, mode, cand_n, cand) <= 227 * 1024) { s = cand; break; }
+        if (s != 0) { n = cand_n; break; }
+    }
     if (n == 0) return false;
-    int s = 0;
-    for (int cand = tuning_int("TVDCN_B200_FWD_STAGES", 3); cand >= 2; --cand)
-        if (fwd_tc_smem_bytes(dim, mode, n, cand) <= 227 * 1024) { s = cand; break; }
-    if (s == 0) return false;
     *bn = n;
     *stages = s;
     return true;
