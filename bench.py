@@ -309,11 +309,14 @@ def peaks():
 
 def known_traffic(kernel: str, config: int, mode: str):
     """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
-    under profiles/ (config2_bf16_tensor_kernels.md); None where no capture exists."""
+    under profiles/ (config2_tensor_kernels.md); None where no capture exists."""
     table = {
-        'dcn_fwd_tc/cfg2/bf16': 85.20e6 + 22.62e6,
-        'dcn_dgrad_tc/cfg2/bf16': 272.26e6 + 91.69e6,
-        'dcn_wgrad_tc/cfg2/bf16': 137.70e6 + 4.09e6,
+        'dcn_fwd_tc/cfg2/bf16': 85.14e6 + 22.25e6,
+        'dcn_dgrad_tc/cfg2/bf16': 272.38e6 + 90.03e6,
+        'dcn_wgrad_tc/cfg2/bf16': 137.70e6 + 3.46e6,
+        'dcn_fwd_tc/cfg2/fp32': 137.83e6 + 68.71e6,
+        'dcn_dgrad_tc/cfg2/fp32': 377.43e6 + 104.86e6,
+        'dcn_wgrad_tc/cfg2/fp32': 245.56e6 + 9.95e6,
     }
     return table.get(f'{kernel}/cfg{config}/{mode}')
 
