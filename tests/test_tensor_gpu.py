@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import cases
-from cases import Case, make_inputs, nerr, run_oracle
+from cases import Case, make_inputs, nerr, run_cabi, run_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -109,3 +109,29 @@ def test_transposed_all_tensor(dtype, tol):
     cases.assert_parity(got, ref, tol, case.name)
     from tvdcn_b200 import cabi
     assert cabi.lib().tvdcn_b200_device_status() == 0
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16], ids=['f32split', 'bf16'])
+def test_non_finite_pixel_does_not_leak_through_out_of_image_corners(dtype):
+    """An Inf at pixel 0 of the image must reach only the results that sample that pixel, as in the reference,
+    which never reads an out-of-image corner: the tensor-core kernels read a row of zeros there instead of
+    multiplying whatever pixel 0 holds by a zero weight."""
+    from oracle import build_ref
+    if not build_ref.load():
+        pytest.skip('oracle/_ref is not built')
+    case = Case('inf_pixel', 2, False, 2, 64, 64, (8, 8), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 1, 1, True, 3.0)
+    x, w, off, mask, bias, go = make_inputs(case, seed=9, dtype=torch.float32)
+    x[0, :, 0, 0] = float('inf')
+    q = lambda t: t.to(dtype)
+    ref = cases.run_reference(case, q(x).float(), q(w).float(), off, mask, bias, q(go).float())
+    got = run_cabi(case, q(x).cuda(), q(w).cuda(), off.cuda(), mask.cuda(), bias.cuda(), q(go).cuda(),
+                   engine=2)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    for name, a, r in zip(cases.NAMES, got, ref):
+        a = a.float().cpu()
+        fin = torch.isfinite(r)
+        assert fin.any(), name
+        assert torch.equal(torch.isfinite(a), fin), f'{name}: non-finite values in different places'
+        scale = float(r[fin].abs().max())
+        err = float((a[fin] - r[fin]).abs().max()) / max(scale, 1e-30)
+        assert err <= tol, f'{name}: {err:.3e}'

@@ -161,6 +161,11 @@ static cudaError_t stage_image(const tvdcn_problem *p, const GeoHost &g, const P
     if (t_staged_image == img) return cudaSuccess;
     const int es = p->dtype == TVDCN_F32 ? 4 : 2;
     cudaError_t e = launch_to_channels_last(img, ws + pl.img_cl, g.B, g.Cs, g.S, es, stream);
+    // Row B*S of the staged image is all zeros: corners that fall outside the image (and the positions past the
+    // end of the last tile) read it, so that an Inf or NaN elsewhere in the image cannot leak into results that
+    // the reference computes without touching that pixel (0 x Inf = NaN).
+    if (e == cudaSuccess)
+        e = cudaMemsetAsync(ws + pl.img_cl + (size_t)g.B * g.S * g.Cs * es, 0, (size_t)g.Cs * es, stream);
     if (e == cudaSuccess) t_staged_image = img;
     return e;
 }

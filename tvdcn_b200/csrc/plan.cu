@@ -27,7 +27,7 @@ const char *tc_common(const tvdcn_problem *p, const GeoHost &g) {
     if (cdg % 64 != 0) return "dense channels per group must be a multiple of 64";
     if (g.og > 0 && (g.Cs / g.og) % 64 != 0) return "channels per offset group must be a multiple of 64";
     if (g.mg > 0 && (g.Cs / g.mg) % 64 != 0) return "channels per mask group must be a multiple of 64";
-    if ((long long)g.B * g.S * g.Cs >= (1LL << 31) || (long long)g.B * g.P >= (1LL << 31))
+    if (((long long)g.B * g.S + 1) * g.Cs >= (1LL << 31) || (long long)g.B * g.P >= (1LL << 31))
         return "sampled image has 2^31 elements or more (32-bit element offsets)";
     return nullptr;
 }
@@ -70,7 +70,7 @@ Plan plan_forward(const tvdcn_problem *p) {
     if (why == nullptr && !p->transposed) {
         if (fwd_tc_config(g.dim, mode, g.Cd / g.groups, &bn, &st) && chain_ok(mode, g, bn)) {
             pl.tensor = pl.tc_sg = true;
-            pl.img_cl = b.take((size_t)g.B * g.S * g.Cs * es);
+            pl.img_cl = b.take(((size_t)g.B * g.S + 1) * g.Cs * es);   // + one row of zeros, see stage_image
             pl.w_pack = b.take(nw * 2);
             if (p->dtype == TVDCN_F32) pl.w_pack_lo = b.take(nw * 2);
         } else {
@@ -125,7 +125,7 @@ Plan plan_backward(const tvdcn_problem *p, bool want_input, bool want_weight, bo
             take_scatter_buffers(pl, b, p, g, scatter);
         }
         pl.tensor = pl.tc_sg || pl.tc_sw || pl.tc_gs;
-        if (pl.tensor) pl.img_cl = b.take((size_t)g.B * g.S * g.Cs * es);
+        if (pl.tensor) pl.img_cl = b.take(((size_t)g.B * g.S + 1) * g.Cs * es);
         if (!pl.tensor) pl.why_not = "no tensor-core kernel covers the requested gradients for this shape";
     } else {
         pl.why_not = why;

@@ -165,7 +165,8 @@ __device__ __forceinline__ void build_plan(const Geo<DIM> &g, const PosInfo<DIM>
             w *= bit ? fr[a] : (1.f - fr[a]);
         }
         PlanEntry e;
-        e.row16 = ok ? (uint32_t)(pi.b * g.S + flat) * row_scale : 0u;
+        // out-of-image corners read the row of zeros that follows the staged image
+        e.row16 = (uint32_t)(ok ? pi.b * g.S + flat : g.B * g.S) * row_scale;
         e.w = encode_weight<MODE>(ok ? w : 0.f);
         slot[c] = e;
     }

@@ -147,7 +147,7 @@ __device__ __forceinline__ void corner_of(const Geo<DIM> &g, const PosInfo<DIM> 
         flat = flat * g.img[a] + i;
         w *= bit ? tg.fr[a] : (1.f - tg.fr[a]);
     }
-    rowi = ok ? pi.b * g.S + flat : 0;
+    rowi = ok ? pi.b * g.S + flat : g.B * g.S;   // the row of zeros after the staged image (never scattered to: w = 0)
     if (!ok) w = 0.f;
 }
 
