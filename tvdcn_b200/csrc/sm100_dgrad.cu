@@ -775,6 +775,94 @@ __global__ void __launch_bounds__(256) to_channels_last_split_kernel(const float
     }
 }
 
+// [B, C, S] f32 -> [B, S, C] bf16 hi + lo with 16-byte loads and 4-byte (channel pair) stores, for S a multiple of 4
+// and C of 2; 64 x 64 tiles.  Even channels sit in rows 0-31 of the shared tile, odd ones in rows 32-63, so that the
+// transposing reads of a channel pair per lane are free of bank conflicts.
+__global__ void __launch_bounds__(256) to_channels_last_split64_kernel(const float *__restrict__ src,
+                                                                       uint32_t *__restrict__ hi,
+                                                                       uint32_t *__restrict__ lo, int C, int S) {
+    __shared__ float tile[64 * 65];
+    const int b = blockIdx.z;
+    const int s0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
+    const float *in = src + (int64_t)b * C * S;
+    const int v = threadIdx.x & 15, r = threadIdx.x >> 4;
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int cl = pass * 16 + r;
+        const int c = c0 + cl, s = s0 + v * 4;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < C && s < S) x = __ldg(reinterpret_cast<const float4 *>(in + (int64_t)c * S + s));
+        float *w = tile + ((cl >> 1) + 32 * (cl & 1)) * 65 + v * 4;
+        w[0] = x.x;
+        w[1] = x.y;
+        w[2] = x.z;
+        w[3] = x.w;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c = c0 + 2 * lane;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int sl = warp * 8 + i;
+        const int s = s0 + sl;
+        if (c < C && s < S) {
+            const float a = tile[lane * 65 + sl], bb = tile[(32 + lane) * 65 + sl];
+            const __nv_bfloat16 ha = __float2bfloat16_rn(a), hb = __float2bfloat16_rn(bb);
+            const __nv_bfloat16 la = __float2bfloat16_rn(a - __bfloat162float(ha));
+            const __nv_bfloat16 lb = __float2bfloat16_rn(bb - __bfloat162float(hb));
+            const int64_t o = ((int64_t)b * C * S + (int64_t)s * C + c) >> 1;
+            hi[o] = (uint32_t)__bfloat16_as_ushort(ha) | ((uint32_t)__bfloat16_as_ushort(hb) << 16);
+            lo[o] = (uint32_t)__bfloat16_as_ushort(la) | ((uint32_t)__bfloat16_as_ushort(lb) << 16);
+        }
+    }
+}
+
+// [B, S, C] f32 (+ bias[c]) -> [B, C, S] with 16-byte loads and 4-element stores, for S and C multiples of 4
+template <typename TO>
+__global__ void __launch_bounds__(256) from_channels_last_bias64_kernel(const float *__restrict__ src,
+                                                                        const float *__restrict__ bias,
+                                                                        TO *__restrict__ dst, int C, int S) {
+    __shared__ float tile[64 * 65];
+    const int b = blockIdx.z;
+    const int s0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
+    const float *in = src + (int64_t)b * C * S;
+    TO *out = dst + (int64_t)b * C * S;
+    const int v = threadIdx.x & 15, r = threadIdx.x >> 4;
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int sl = pass * 16 + r;
+        const int s = s0 + sl, c = c0 + v * 4;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < C && s < S) x = __ldg(reinterpret_cast<const float4 *>(in + (int64_t)s * C + c));
+        float *w = tile + sl * 65 + v * 4;
+        w[0] = x.x;
+        w[1] = x.y;
+        w[2] = x.z;
+        w[3] = x.w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int cl = pass * 16 + r;
+        const int c = c0 + cl, s = s0 + v * 4;
+        if (c < C && s < S) {
+            const float bv = bias != nullptr ? __ldg(bias + c) : 0.f;
+            float x[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) x[k] = tile[(v * 4 + k) * 65 + cl] + bv;
+            TO *o = out + (int64_t)c * S + s;
+            if constexpr (sizeof(TO) == 4) {
+                *reinterpret_cast<float4 *>(o) = make_float4(x[0], x[1], x[2], x[3]);
+            } else {
+                TO y[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) store_acc(y, k, x[k]);
+                *reinterpret_cast<uint2 *>(o) = *reinterpret_cast<const uint2 *>(y);
+            }
+        }
+    }
+}
+
 // [B, S, C] f32 (+ bias[c]) -> [B, C, S] in the destination type
 template <typename TO>
 __global__ void __launch_bounds__(256) from_channels_last_bias_kernel(const float *__restrict__ src,
@@ -844,7 +932,13 @@ cudaError_t launch_to_channels_last_split(const float *src, void *hi, void *lo, 
                                           cudaStream_t stream) {
     dim3 grid((S + 31) / 32, (C + 31) / 32, B);
     LaunchScope scope("to_channels_last", stream);
-    to_channels_last_split_kernel<<<grid, 256, 0, stream>>>(src, (__nv_bfloat16 *)hi, (__nv_bfloat16 *)lo, C, S);
+    if (S % 4 == 0 && C % 2 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+        ((reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(lo)) & 3) == 0) {
+        dim3 grid64((S + 63) / 64, (C + 63) / 64, B);
+        to_channels_last_split64_kernel<<<grid64, 256, 0, stream>>>(src, (uint32_t *)hi, (uint32_t *)lo, C, S);
+    } else {
+        to_channels_last_split_kernel<<<grid, 256, 0, stream>>>(src, (__nv_bfloat16 *)hi, (__nv_bfloat16 *)lo, C, S);
+    }
     return cudaGetLastError();
 }
 
@@ -852,7 +946,16 @@ cudaError_t launch_from_channels_last_bias(const float *src, const float *bias, 
                                            int S, cudaStream_t stream) {
     dim3 grid((S + 31) / 32, (C + 31) / 32, B);
     LaunchScope scope("from_channels_last", stream);
-    if (dst_dtype == DT_F32)
+    const bool wide = S % 4 == 0 && C % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+                      (reinterpret_cast<uintptr_t>(dst) & 15) == 0;
+    dim3 grid64((S + 63) / 64, (C + 63) / 64, B);
+    if (dst_dtype == DT_F32 && wide)
+        from_channels_last_bias64_kernel<float><<<grid64, 256, 0, stream>>>(src, bias, (float *)dst, C, S);
+    else if (dst_dtype == DT_BF16 && wide)
+        from_channels_last_bias64_kernel<__nv_bfloat16><<<grid64, 256, 0, stream>>>(src, bias, (__nv_bfloat16 *)dst, C, S);
+    else if (dst_dtype == DT_F16 && wide)
+        from_channels_last_bias64_kernel<__half><<<grid64, 256, 0, stream>>>(src, bias, (__half *)dst, C, S);
+    else if (dst_dtype == DT_F32)
         from_channels_last_bias_kernel<float><<<grid, 256, 0, stream>>>(src, bias, (float *)dst, C, S);
     else if (dst_dtype == DT_BF16)
         from_channels_last_bias_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(src, bias, (__nv_bfloat16 *)dst, C, S);

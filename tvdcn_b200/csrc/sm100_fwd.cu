@@ -472,6 +472,24 @@ __global__ void pack_weight_kernel(const TW *__restrict__ w, int mode, int group
     }
 }
 
+// same, four elements per thread
+__global__ void split_f32_vec4_kernel(const float4 *__restrict__ src, uint2 *__restrict__ hi, uint2 *__restrict__ lo,
+                                      int64_t n4) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 v = __ldg(src + i);
+        const float f[4] = {v.x, v.y, v.z, v.w};
+        uint32_t h[4], l[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const __nv_bfloat16 hb = __float2bfloat16_rn(f[k]);
+            h[k] = __bfloat16_as_ushort(hb);
+            l[k] = __bfloat16_as_ushort(__float2bfloat16_rn(f[k] - __bfloat162float(hb)));
+        }
+        hi[i] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+        lo[i] = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+    }
+}
+
 template <bool KS>
 cudaError_t launch_pack_weight(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
                                void *lo, cudaStream_t stream) {
@@ -515,9 +533,17 @@ cudaError_t launch_pack_weight_kd(const void *w, int dtype, int mode, int groups
 }
 
 cudaError_t launch_split_f32(const float *src, void *hi, void *lo, int64_t n, cudaStream_t stream) {
-    const int blocks = (int)std::min<int64_t>((n + 255) / 256, 148 * 16);
     LaunchScope scope("split_f32", stream);
-    split_f32_kernel<<<blocks, 256, 0, stream>>>(src, (__nv_bfloat16 *)hi, (__nv_bfloat16 *)lo, n);
+    const bool wide = n % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+                      ((reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(lo)) & 7) == 0;
+    if (wide) {
+        const int blocks = (int)std::min<int64_t>((n / 4 + 255) / 256, 148 * 16);
+        split_f32_vec4_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const float4 *>(src), (uint2 *)hi, (uint2 *)lo,
+                                                          n / 4);
+    } else {
+        const int blocks = (int)std::min<int64_t>((n + 255) / 256, 148 * 16);
+        split_f32_kernel<<<blocks, 256, 0, stream>>>(src, (__nv_bfloat16 *)hi, (__nv_bfloat16 *)lo, n);
+    }
     return cudaGetLastError();
 }
 
