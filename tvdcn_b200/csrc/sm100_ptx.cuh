@@ -64,6 +64,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
+// Same bound, with a short sleep between polls: the waiting warp gives its issue slots to the warps that share its
+// scheduler, at the price of a later wake-up.  Pays where the waiters outnumber the workers (measured per kernel).
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t *bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kMaxPolls; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(32);
+    }
+    return false;
+}
 
 // Generic-proxy writes to shared memory (st.shared by the producer threads) must be made visible to the
 // async proxy (tensor-core operand reads) before the MMA is issued.
