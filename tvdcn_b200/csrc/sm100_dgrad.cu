@@ -239,7 +239,10 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int grp = blockIdx.y;
     const long long m0 = (long long)blockIdx.x * TILE_POS;
-    const int n_blocks = g.K * (P.chunks_per_tap / NB);
+    // column blocks of this CTA: gridDim.z CTAs share one position tile and take equal ranges of its (tap, chunk)
+    // blocks, which evens out the last wave when the tiles do not fill the SMs a whole number of times
+    const int n_blocks = g.K * (P.chunks_per_tap / NB) / (int)gridDim.z;
+    const int blk0 = (int)blockIdx.z * n_blocks;
     const bool want_coord = P.goff != nullptr || P.gmask != nullptr;
     const bool deformable = P.offset != nullptr;
 
@@ -286,11 +289,12 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
         const bool scatter = P.img_grad_cl != nullptr;
         int k = 0;  // chunks handled so far: selects the staging buffer
         bool ok = true;
-        for (int blk = 0; blk < n_blocks && ok; ++blk) {
-            const int q = blk % NQ;
+        for (int bi = 0; bi < n_blocks && ok; ++bi) {
+                const int blk = blk0 + bi;
+            const int q = bi % NQ;
             const int tap = blk % g.K;
             const int cc0 = (blk / g.K) * NB;
-            ok = dg_wait<SPLIT>(&t_full[q], (uint32_t)((blk / NQ) & 1));
+            ok = dg_wait<SPLIT>(&t_full[q], (uint32_t)((bi / NQ) & 1));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 if (lane == 0) atomicExch(P.status, 301);
@@ -410,7 +414,8 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
             const int ci0 = 2 * (q8 & 3);             // first of its two 16-byte chunks in that warp's row
             int k = 0;
             bool ok = true;
-            for (int blk = 0; blk < n_blocks && ok; ++blk) {
+            for (int bi = 0; bi < n_blocks && ok; ++bi) {
+                const int blk = blk0 + bi;
                 const int tap = blk % g.K;
                 const int cc0 = (blk / g.K) * NB;
                 for (int ci = 0; ci < NB; ++ci, ++k) {
@@ -569,7 +574,8 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
             const int q4 = lane & 3, p8 = lane >> 2;
             int k = 0;
             bool ok = true;
-            for (int blk = 0; blk < n_blocks && ok; ++blk) {
+            for (int bi = 0; bi < n_blocks && ok; ++bi) {
+                const int blk = blk0 + bi;
                 const int tap = blk % g.K;
                 const int cc0 = (blk / g.K) * NB;
                 for (int ci = 0; ci < NB; ++ci, ++k) {
@@ -677,9 +683,10 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
             if (!ok) atomicExch(P.status, 302);
             const uint32_t a_addr = ptx::smem_u32(sA);
             int j = 0;  // running B stage counter
-            for (int blk = 0; blk < n_blocks && ok; ++blk) {
-                const int q = blk % NQ;
-                if (!dg_wait<SPLIT>(&t_empty[q], (uint32_t)(((blk / NQ) & 1) ^ 1))) {
+            for (int bi = 0; bi < n_blocks && ok; ++bi) {
+                const int blk = blk0 + bi;
+                const int q = bi % NQ;
+                if (!dg_wait<SPLIT>(&t_empty[q], (uint32_t)(((bi / NQ) & 1) ^ 1))) {
                     atomicExch(P.status, 303);
                     ok = false;
                     break;
@@ -726,7 +733,8 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
             }
             int j = 0, issued = 0;
             bool ok = true;
-            for (int blk = 0; blk < n_blocks && ok; ++blk) {
+            for (int bi = 0; bi < n_blocks && ok; ++bi) {
+                const int blk = blk0 + bi;
                 const int tap = blk % g.K;
                 const int cc0 = (blk / g.K) * NB;
                 for (int rc = 0; rc < RC; ++rc, ++j) {
@@ -1010,7 +1018,23 @@ cudaError_t launch_gemm_scatter_tc(const GeoHost &h, int mode, const void *dense
             maps[3] = maps[2];
         }
     }
-    dim3 grid((unsigned)((BP + TILE_POS - 1) / TILE_POS), (unsigned)h.groups);
+    // Share each position tile between `splits` CTAs (equal ranges of its column blocks) when that evens out the
+    // last wave: cost of a launch ~ ceil(CTAs / SMs) / splits tile-times; a split is taken only for a gain above
+    // 4 % (each extra CTA reloads the dense tile).
+    const long long tiles = ((BP + TILE_POS - 1) / TILE_POS) * h.groups;
+    const int n_total = h.K * ((csg / 64) / nb);
+    int splits = 1;
+    {
+        const int forced = tuning_int("TVDCN_B200_DG_SPLITS", 0);
+        double best = (double)((tiles + 147) / 148);
+        for (int cand = 2; cand <= 3; ++cand) {
+            if (n_total % cand != 0) continue;
+            const double cost = (double)((tiles * cand + 147) / 148) / cand;
+            if (cost < best * 0.96) { best = cost; splits = cand; }
+        }
+        if (forced > 0 && n_total % forced == 0) splits = forced;
+    }
+    dim3 grid((unsigned)((BP + TILE_POS - 1) / TILE_POS), (unsigned)h.groups, (unsigned)splits);
     auto run = [&](auto dimc) -> cudaError_t {
         constexpr int DIM = decltype(dimc)::value;
         DgradParams<DIM> P;
