@@ -285,12 +285,23 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
         const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + t);
         const bool deformable = P.offset != nullptr;
         const uint32_t row_scale = (uint32_t)g.Cs * ESZ / 16u;
+        // offsets / mask of chunk j + 2 are requested while chunk j is planned: their latency stays off the
+        // critical path (one planner thread has nothing else in flight)
+        auto coords_of = [&](int j) {
+            const int chan0 = chunk_chan0(j);
+            return load_coords<DIM>(g, pi, P.offset, P.mask, chunk_tap(j), g.og > 0 ? chan0 / g.cs_per_og : 0,
+                                    g.mg > 0 ? chan0 / g.cs_per_mg : 0);
+        };
+        RawCoords<DIM> rc0, rc1, rc2;
+        if (n_chunks > 0) rc0 = coords_of(0);
+        if (n_chunks > 1) rc1 = coords_of(1);
         for (int j = 0; j < n_chunks; ++j) {
             const int pbuf = j % PLAN_BUFS;
             const int tap = chunk_tap(j), chan0 = chunk_chan0(j);
-            const int ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
-            const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
-            const RawCoords<DIM> rc = load_coords<DIM>(g, pi, P.offset, P.mask, tap, ogi, mgi);
+            if (j + 2 < n_chunks) rc2 = coords_of(j + 2);
+            const RawCoords<DIM> rc = rc0;
+            rc0 = rc1;
+            rc1 = rc2;
             bool ok = ptx::mbar_wait(&plan_empty[pbuf], (uint32_t)(((j / PLAN_BUFS) & 1) ^ 1));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {

@@ -283,20 +283,33 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
             e_mg[k] = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
         }
         const int slot = t % WG_POS;
-        for (int i = 0; i < n_stages; ++i) {
-            const int pb = i % WG_PLAN_BUFS;
-            const int pc = chunk_begin + i;
-            const int p = (pc % P.chunks_per_image) * WG_POS + slot;
+        // offsets / mask of stage i + 2 are requested while stage i is planned, so that their latency stays off
+        // the critical path
+        struct StageCoords {
             PosInfo<DIM> pi[EPT];
             RawCoords<DIM> rc[EPT];
+        };
+        auto fetch = [&](int i, StageCoords &sc) {
+            const int pc = chunk_begin + i;
+            const int p = (pc % P.chunks_per_image) * WG_POS + slot;
 #pragma unroll
             for (int k = 0; k < EPT; ++k) {
-                pi[k].valid = e_ok[k] && p < g.P;
-                pi[k].b = pc / P.chunks_per_image;
-                pi[k].p = pi[k].valid ? p : 0;
-                decode_in_image<DIM>(g, pi[k]);
-                if (e_on[k]) rc[k] = load_coords<DIM>(g, pi[k], P.offset, P.mask, e_tap[k], e_og[k], e_mg[k]);
+                sc.pi[k].valid = e_ok[k] && p < g.P;
+                sc.pi[k].b = pc / P.chunks_per_image;
+                sc.pi[k].p = sc.pi[k].valid ? p : 0;
+                decode_in_image<DIM>(g, sc.pi[k]);
+                if (e_on[k]) sc.rc[k] = load_coords<DIM>(g, sc.pi[k], P.offset, P.mask, e_tap[k], e_og[k], e_mg[k]);
             }
+        };
+        StageCoords c0, c1, c2;
+        if (n_stages > 0) fetch(0, c0);
+        if (n_stages > 1) fetch(1, c1);
+        for (int i = 0; i < n_stages; ++i) {
+            const int pb = i % WG_PLAN_BUFS;
+            if (i + 2 < n_stages) fetch(i + 2, c2);
+            const StageCoords cur = c0;
+            c0 = c1;
+            c1 = c2;
             bool ok = ptx::mbar_wait(&plan_empty[pb], (uint32_t)(((i / WG_PLAN_BUFS) & 1) ^ 1));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
@@ -306,7 +319,7 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
 #pragma unroll
             for (int k = 0; k < EPT; ++k) {
                 if (e_on[k])
-                    build_plan<DIM, MODE>(g, pi[k], rc[k], deformable, e_tap[k], row_scale,
+                    build_plan<DIM, MODE>(g, cur.pi[k], cur.rc[k], deformable, e_tap[k], row_scale,
                                           plan + ((pb * NS) * WG_POS + t + k * WG_PLANNERS) * NC);
             }
             __syncwarp();
