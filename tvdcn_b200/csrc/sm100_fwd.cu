@@ -89,7 +89,12 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
     // f32 data: the tensor core's f32 accumulation rounds toward zero, so the error of one accumulator grows
     // with the number of MMAs added into it.  Chunks go round-robin into NACC accumulators, which the epilogue
     // adds (round to nearest); this divides the chain length by NACC.
-    const int NACC = SPLIT ? min(4, 512 / BN) : 1;
+    // As many accumulators as keep one chain near 250 MMAs (12 per chunk), at most 4 and what 512 columns hold.
+    int NACC = 1;
+    if (SPLIT) {
+        NACC = min(min(4, 512 / BN), (n_chunks * 12 + 249) / 250);
+        NACC = NACC == 3 ? 2 : max(NACC, 1);          // the column count must be a power of two
+    }
     const uint32_t ncols = (uint32_t)(NACC * BN) < 32u ? 32u : (uint32_t)(NACC * BN);
 
     if (threadIdx.x == 0) {
