@@ -43,9 +43,16 @@ namespace {
 
 constexpr int PRODUCER_WARPS = 16;
 constexpr int PRODUCERS = PRODUCER_WARPS * 32;
-constexpr int PGROUPS = 2;                        // producer groups; group q samples chunks j with j % PGROUPS == q
-constexpr int GROUP_WARPS = PRODUCER_WARPS / PGROUPS;
-constexpr int GROUP_THREADS = GROUP_WARPS * 32;
+// Producer groups: group q samples chunks j with j % groups == q.  Two groups for 16-bit data (three stages: one
+// group's gathers are in flight while the other blends); one group of all 16 warps for f32 data, whose two stages
+// would otherwise make each group wait for the MMA of its own previous chunk.
+__host__ __device__ constexpr int producer_groups_of(int mode) {
+#ifdef TVDCN_FWD_GROUPS_SPLIT
+    return mode == TC_SPLIT ? TVDCN_FWD_GROUPS_SPLIT : 2;
+#else
+    return mode == TC_SPLIT ? 1 : 2;
+#endif
+}
 constexpr int PLANNER_WARPS = 4;                  // one planner thread per tile position
 constexpr int PLAN_BUFS = 4;
 constexpr int FWD_THREADS = PRODUCERS + 64 + PLANNER_WARPS * 32;
@@ -57,6 +64,9 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
     constexpr int NC = 1 << DIM;
     constexpr bool SPLIT = MODE == TC_SPLIT;
     constexpr int PARTS = SPLIT ? 2 : 1;
+    constexpr int PGROUPS = producer_groups_of(MODE);
+    constexpr int GROUP_WARPS = PRODUCER_WARPS / PGROUPS;
+    constexpr int GROUP_THREADS = GROUP_WARPS * 32;
     using T16 = typename std::conditional<MODE == TC_F16, __half, __nv_bfloat16>::type;
     const Geo<DIM> &g = P.g;
 
