@@ -443,29 +443,6 @@ __global__ void __launch_bounds__(256) to_channels_last32_kernel(const uint32_t 
     }
 }
 
-// [B, S, C] f32 -> [B, C, S] in the destination type.
-template <typename TO>
-__global__ void __launch_bounds__(256) from_channels_last_kernel(const float *__restrict__ src, TO *__restrict__ dst,
-                                                                 int C, int S) {
-    __shared__ float tile[32][33];
-    const int b = blockIdx.z;
-    const int s0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
-    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-    const float *in = src + (int64_t)b * C * S;
-    TO *out = dst + (int64_t)b * C * S;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int s = s0 + ty + 8 * i, c = c0 + tx;
-        if (c < C && s < S) tile[ty + 8 * i][tx] = in[(int64_t)s * C + c];
-    }
-    __syncthreads();
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int c = c0 + ty + 8 * i, s = s0 + tx;
-        if (c < C && s < S) store_acc(out, (int64_t)c * S + s, tile[tx][ty + 8 * i]);
-    }
-}
-
 // weight [Cd, csg, K] -> hi/lo [g][tap][d'][s'] (KS = true) or [g][tap][s'][d'] (KS = false)
 template <typename TW, bool KS>
 __global__ void pack_weight_kernel(const TW *__restrict__ w, int mode, int groups, int cdg, int csg, int K,
@@ -589,21 +566,6 @@ cudaError_t launch_to_channels_last(const void *src, void *dst, int B, int C, in
         to_channels_last32_kernel<<<grid64, 256, 0, stream>>>((const uint32_t *)src, (uint32_t *)dst, C, S);
     } else if (elem_bytes == 4)
         to_channels_last_kernel<uint32_t><<<grid, 256, 0, stream>>>((const uint32_t *)src, (uint32_t *)dst, C, S);
-    else
-        return cudaErrorInvalidValue;
-    return cudaGetLastError();
-}
-
-cudaError_t launch_from_channels_last_f32(const float *src, void *dst, int dst_dtype, int B, int C, int S,
-                                          cudaStream_t stream) {
-    dim3 grid((S + 31) / 32, (C + 31) / 32, B);
-    LaunchScope scope("from_channels_last", stream);
-    if (dst_dtype == DT_F32)
-        from_channels_last_kernel<float><<<grid, 256, 0, stream>>>(src, (float *)dst, C, S);
-    else if (dst_dtype == DT_BF16)
-        from_channels_last_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(src, (__nv_bfloat16 *)dst, C, S);
-    else if (dst_dtype == DT_F16)
-        from_channels_last_kernel<__half><<<grid, 256, 0, stream>>>(src, (__half *)dst, C, S);
     else
         return cudaErrorInvalidValue;
     return cudaGetLastError();
