@@ -1,8 +1,9 @@
 """Softmax over the kernel taps of each mask group.
 
-Same signatures as tvdcn/ops/activations/mask_softmax.py:19-184, and scriptable like them.  CUDA tensors go
-through the ``tvdcn::mask_softmax{1,2,3}d`` operators (single-pass kernel, forward and backward); other
-tensors use the reference's own definition, a ``torch.softmax`` over the tap axis of the grouped view.
+Same signatures as tvdcn/ops/activations/mask_softmax.py:19-184, and scriptable like them.  Every call goes
+through the ``tvdcn::mask_softmax{1,2,3}d`` operators (single-pass CUDA kernel, forward and backward).  Like the
+convolution operators they have CUDA kernels only: a CPU tensor is refused by the dispatcher, there is no
+fallback to ``torch.softmax``.
 """
 from typing import Optional, Tuple
 
@@ -33,12 +34,8 @@ def mask_softmax1d(mask: Tensor, kernel_size: Tuple[int]) -> Tensor:
         kernel_size = _single(kernel_size)
     taps = kernel_size[0]
     _check_mask(mask, taps, 1)
-    if mask.is_cuda:
-        _assert_has_ops()
-        return torch.ops.tvdcn.mask_softmax1d(mask, [kernel_size[0]])
-    groups = mask.size(1) // taps
-    view = mask.view(mask.size(0), groups, taps, mask.size(2))
-    return torch.softmax(view, dim=2).view(mask.size(0), groups * taps, mask.size(2))
+    _assert_has_ops()
+    return torch.ops.tvdcn.mask_softmax1d(mask, [kernel_size[0]])
 
 
 def mask_softmax2d(mask: Tensor, kernel_size: Tuple[int, int]) -> Tensor:
@@ -47,12 +44,8 @@ def mask_softmax2d(mask: Tensor, kernel_size: Tuple[int, int]) -> Tensor:
         kernel_size = _pair(kernel_size)
     taps = kernel_size[0] * kernel_size[1]
     _check_mask(mask, taps, 2)
-    if mask.is_cuda:
-        _assert_has_ops()
-        return torch.ops.tvdcn.mask_softmax2d(mask, [kernel_size[0], kernel_size[1]])
-    groups = mask.size(1) // taps
-    view = mask.view(mask.size(0), groups, taps, mask.size(2), mask.size(3))
-    return torch.softmax(view, dim=2).view(mask.size(0), groups * taps, mask.size(2), mask.size(3))
+    _assert_has_ops()
+    return torch.ops.tvdcn.mask_softmax2d(mask, [kernel_size[0], kernel_size[1]])
 
 
 def mask_softmax3d(mask: Tensor, kernel_size: Tuple[int, int, int]) -> Tensor:
@@ -61,12 +54,8 @@ def mask_softmax3d(mask: Tensor, kernel_size: Tuple[int, int, int]) -> Tensor:
         kernel_size = _triple(kernel_size)
     taps = kernel_size[0] * kernel_size[1] * kernel_size[2]
     _check_mask(mask, taps, 3)
-    if mask.is_cuda:
-        _assert_has_ops()
-        return torch.ops.tvdcn.mask_softmax3d(mask, [kernel_size[0], kernel_size[1], kernel_size[2]])
-    groups = mask.size(1) // taps
-    view = mask.view(mask.size(0), groups, taps, mask.size(2), mask.size(3), mask.size(4))
-    return torch.softmax(view, dim=2).view(mask.size(0), groups * taps, mask.size(2), mask.size(3), mask.size(4))
+    _assert_has_ops()
+    return torch.ops.tvdcn.mask_softmax3d(mask, [kernel_size[0], kernel_size[1], kernel_size[2]])
 
 
 class _MaskSoftmaxNd(nn.Module):
