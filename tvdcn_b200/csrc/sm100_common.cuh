@@ -124,20 +124,40 @@ __device__ __forceinline__ uint32_t encode_weight(float w) {
     }
 }
 
-// Writes the NC plan entries of one position.  row_scale = Cs * element size / 16.
-template <int DIM, int MODE>
-__device__ __forceinline__ void build_plan(const Geo<DIM> &g, const PosInfo<DIM> &pi, const RawCoords<DIM> &rc,
-                                           bool deformable, int tap, uint32_t row_scale, PlanEntry *slot) {
-    constexpr int NC = 1 << DIM;
-    int fl[DIM];
-    float fr[DIM];
+// Kernel coordinates of a tap (axis 0 outermost).
+template <int DIM>
+__device__ __forceinline__ void tap_coords(const Geo<DIM> &g, int tap, int (&tc)[DIM]) {
     int r = tap;
-    int tc[DIM];
 #pragma unroll
     for (int a = DIM - 1; a >= 0; --a) {
         tc[a] = r % g.ker[a];
         r /= g.ker[a];
     }
+}
+
+template <int DIM, int MODE>
+__device__ __forceinline__ void build_plan_at(const Geo<DIM> &g, const PosInfo<DIM> &pi, const RawCoords<DIM> &rc,
+                                              bool deformable, const int (&tc)[DIM], uint32_t row_scale,
+                                              PlanEntry *slot);
+
+// Writes the NC plan entries of one position.  row_scale = Cs * element size / 16.
+template <int DIM, int MODE>
+__device__ __forceinline__ void build_plan(const Geo<DIM> &g, const PosInfo<DIM> &pi, const RawCoords<DIM> &rc,
+                                           bool deformable, int tap, uint32_t row_scale, PlanEntry *slot) {
+    int tc[DIM];
+    tap_coords<DIM>(g, tap, tc);
+    build_plan_at<DIM, MODE>(g, pi, rc, deformable, tc, row_scale, slot);
+}
+
+// Same, with the tap's kernel coordinates already known: the divisions by the kernel extents are a quarter of
+// the instructions of a plan entry, and a planner thread makes entries back to back.
+template <int DIM, int MODE>
+__device__ __forceinline__ void build_plan_at(const Geo<DIM> &g, const PosInfo<DIM> &pi, const RawCoords<DIM> &rc,
+                                              bool deformable, const int (&tc)[DIM], uint32_t row_scale,
+                                              PlanEntry *slot) {
+    constexpr int NC = 1 << DIM;
+    int fl[DIM];
+    float fr[DIM];
 #pragma unroll
     for (int a = 0; a < DIM; ++a) {
         const int base = pi.base[a] + tc[a] * g.dil[a];

@@ -47,8 +47,8 @@ constexpr int PRODUCERS = PRODUCER_WARPS * 32;
 // group's gathers are in flight while the other blends); one group of all 16 warps for f32 data, whose two stages
 // would otherwise make each group wait for the MMA of its own previous chunk.
 __host__ __device__ constexpr int producer_groups_of(int mode) {
-#ifdef TVDCN_FWD_GROUPS_SPLIT
-    return mode == TC_SPLIT ? TVDCN_FWD_GROUPS_SPLIT : 2;
+#ifdef TVDCN_FWD_GROUPS_16
+    return mode == TC_SPLIT ? 1 : TVDCN_FWD_GROUPS_16;
 #else
     return mode == TC_SPLIT ? 1 : 2;
 #endif
@@ -56,6 +56,7 @@ __host__ __device__ constexpr int producer_groups_of(int mode) {
 constexpr int PLANNER_WARPS = 4;                  // one planner thread per tile position
 constexpr int PLAN_BUFS = 4;
 constexpr int FWD_THREADS = PRODUCERS + 64 + PLANNER_WARPS * 32;
+constexpr int FWD_MAX_TAPS = 512;                 // taps whose kernel coordinates a CTA tabulates (more: SIMT kernels)
 
 template <int DIM, int MODE>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
@@ -90,6 +91,14 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
     uint64_t *plan_empty = plan_full + PLAN_BUFS;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(plan_empty + PLAN_BUFS);
 
+    // kernel coordinates of every tap, so that the planners do not divide by the kernel extents per chunk
+    __shared__ int16_t tap_tab[FWD_MAX_TAPS * DIM];
+    for (int tp = threadIdx.x; tp < g.K; tp += FWD_THREADS) {
+        int tc[DIM];
+        tap_coords<DIM>(g, tp, tc);
+#pragma unroll
+        for (int a = 0; a < DIM; ++a) tap_tab[tp * DIM + a] = (int16_t)tc[a];
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = g.cdg / BN;
     const int grp = blockIdx.y / tiles_n;
@@ -302,10 +311,21 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
         const uint32_t row_scale = (uint32_t)g.Cs * ESZ / 16u;
         // offsets / mask of chunk j + 2 are requested while chunk j is planned: their latency stays off the
         // critical path (one planner thread has nothing else in flight)
+        // this thread's position is fixed: its offset / mask addresses differ per chunk by a multiple of P only
+        const float *off_base = (P.offset != nullptr && pi.valid)
+                                    ? P.offset + (int64_t)pi.b * g.og * g.K * DIM * (int64_t)g.P + pi.p : nullptr;
+        const float *mask_base = (P.mask != nullptr && pi.valid)
+                                     ? P.mask + (int64_t)pi.b * g.mg * g.K * (int64_t)g.P + pi.p : nullptr;
         auto coords_of = [&](int j) {
-            const int chan0 = chunk_chan0(j);
-            return load_coords<DIM>(g, pi, P.offset, P.mask, chunk_tap(j), g.og > 0 ? chan0 / g.cs_per_og : 0,
-                                    g.mg > 0 ? chan0 / g.cs_per_mg : 0);
+            const int chan0 = chunk_chan0(j), tap = chunk_tap(j);
+            RawCoords<DIM> rc;
+            const int ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
+            const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
+#pragma unroll
+            for (int a = 0; a < DIM; ++a)
+                rc.off[a] = off_base != nullptr ? __ldg(off_base + (int64_t)((ogi * g.K + tap) * DIM + a) * g.P) : 0.f;
+            rc.m = mask_base != nullptr ? __ldg(mask_base + (int64_t)(mgi * g.K + tap) * g.P) : 1.f;
+            return rc;
         };
         RawCoords<DIM> rc0, rc1, rc2;
         if (n_chunks > 0) rc0 = coords_of(0);
@@ -324,7 +344,10 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                 break;
             }
             PlanEntry *slot = plan + (pbuf * TILE_POS + t) * NC;
-            build_plan<DIM, MODE>(g, pi, rc, deformable, tap, row_scale, slot);
+            int tc[DIM];
+#pragma unroll
+            for (int a = 0; a < DIM; ++a) tc[a] = tap_tab[tap * DIM + a];
+            build_plan_at<DIM, MODE>(g, pi, rc, deformable, tc, row_scale, slot);
             const uint4 *row0 = img16 + (uint32_t)chan0 * ESZ / 16u;
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
@@ -618,6 +641,9 @@ size_t fwd_tc_smem_bytes(int dim, int mode, int bn, int stages) {
     return 1024 + stages * stage + plan + (3 * stages + 1 + 2 * PLAN_BUFS) * 8 + 16;
 }
 
+// statically allocated shared memory of the kernel (tap table), which counts against the same 227 KB
+static size_t fwd_static_smem(int dim) { return (size_t)FWD_MAX_TAPS * dim * sizeof(int16_t) + 64; }
+
 // Picks the dense-channel tile and the pipeline depth; returns false when the shape is not covered.
 bool fwd_tc_config(int dim, int mode, int cdg, int *bn, int *stages) {
     const int cap = mode == TC_SPLIT ? tuning_int("TVDCN_B200_FWD_BN_SPLIT", 256) : 256;
@@ -627,7 +653,7 @@ bool fwd_tc_config(int dim, int mode, int cdg, int *bn, int *stages) {
     for (int cand_n : {256, 128, 64}) {
         if (cand_n > cap || cdg % cand_n != 0) continue;
         for (int cand = tuning_int("TVDCN_B200_FWD_STAGES", 3); cand >= 2; --cand)
-            if (fwd_tc_smem_bytes(dim, mode, cand_n, cand) <= 227 * 1024) { s = cand; break; }
+            if (fwd_tc_smem_bytes(dim, mode, cand_n, cand) + fwd_static_smem(dim) <= 227 * 1024) { s = cand; break; }
         if (s != 0) { n = cand_n; break; }
     }
     if (n == 0) return false;
