@@ -37,6 +37,7 @@ struct FwdParams {
     int chunks_per_tap;     // csg / 64
     int prefetch;           // planners also issue L1 prefetches of the corner rows
     long long *prof;        // optional cycle counters of CTA 0 (tuning aid), else null
+    long long *trace;       // optional per-chunk event times of the middle CTA [8 events][64 chunks], else null
 };
 
 namespace {
@@ -148,6 +149,10 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
     // same slab of the image, which then stays in L1 for all of them
     auto chunk_tap = [&](int j) { return j % g.K; };
     auto chunk_chan0 = [&](int j) { return grp * g.csg + (j / g.K) * CHUNK_C; };
+    const bool trace_cta = P.trace != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0;
+    auto mark = [&](int ev, int j) {
+        if (trace_cta && j < 64) P.trace[ev * 64 + j] = clock64();
+    };
 
     if (warp < PRODUCER_WARPS) {
         // ------------------------------------------------------------------ producers
@@ -166,6 +171,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
             const int s = j % S, r = j / S;
             const int pbuf = j % PLAN_BUFS;
             if (prof_on) t0 = clock64();
+            if (tg == 0) mark(6, j);
             if (ok && !ptx::mbar_wait(&plan_full[pbuf], (uint32_t)((j / PLAN_BUFS) & 1))) {
                 atomicExch(P.status, 105);
                 ok = false;
@@ -178,6 +184,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
             ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the __syncwarp below
             if (prof_on) { const long long t1 = clock64(); t_wait += t1 - t0; t0 = t1; }
             if (!ok) break;
+            if (tg == 0) mark(1, j);
             uint8_t *a_hi = sA + (size_t)s * a_stage_bytes;
             const uint32_t c16 = (uint32_t)chunk_chan0(j) * ESZ / 16u;
             produce_tiles<NC, MODE, GROUP_THREADS, 2>(a_hi, a_hi + A_TILE_BYTES, 0u, TILE_POS, TILE_POS, img16, &c16,
@@ -189,6 +196,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                 ptx::mbar_arrive(&full_a[s]);
                 ptx::mbar_arrive(&plan_empty[pbuf]);
             }
+            if (tg == 0) mark(2, j);
             if (prof_on) { const long long t1 = clock64(); t_sig += t1 - t0; t0 = t1; }
         }
         if (prof_on) {
@@ -255,6 +263,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                     break;
                 }
                 ptx::tc_fence_after();
+                mark(3, j);
                 const uint32_t a_addr = ptx::smem_u32(sA + (size_t)s * a_stage_bytes);
                 const uint32_t b_addr = ptx::smem_u32(sB + (size_t)s * b_stage_bytes);
 #pragma unroll
@@ -271,6 +280,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                     }
                 }
                 ptx::mma_commit(&empty[s]);
+                mark(4, j);
             }
             if (ok) ptx::mma_commit(accum);
         }
@@ -288,6 +298,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                 const int tap = j % g.K, cc = j / g.K;
                 uint8_t *b_dst = sB + (size_t)s * b_stage_bytes;
                 ptx::mbar_arrive_expect_tx(&full_b[s], b_stage_bytes);
+                mark(5, j);
                 ptx::tma_load_4d(b_dst, &tmap_hi, &full_b[s], cc * CHUNK_C, n0, tap, grp);
                 if (SPLIT) ptx::tma_load_4d(b_dst + b_part_bytes, &tmap_lo, &full_b[s], cc * CHUNK_C, n0, tap, grp);
                 issued = j + 1;
@@ -316,50 +327,88 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                                     ? P.offset + (int64_t)pi.b * g.og * g.K * DIM * (int64_t)g.P + pi.p : nullptr;
         const float *mask_base = (P.mask != nullptr && pi.valid)
                                      ? P.mask + (int64_t)pi.b * g.mg * g.K * (int64_t)g.P + pi.p : nullptr;
-        auto coords_of = [&](int j) {
-            const int chan0 = chunk_chan0(j), tap = chunk_tap(j);
+        // (tap, channel chunk) of the chunk being planned and of the chunk whose coordinates are being requested,
+        // advanced by counting: a planner thread runs one dependent instruction chain, so every division in it
+        // costs the whole CTA
+        struct Cursor {
+            int tap, cc, ogi, mgi;
+        };
+        auto settle = [&](Cursor &c) {
+            const int chan0 = grp * g.csg + c.cc * CHUNK_C;
+            c.ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
+            c.mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
+        };
+        auto advance = [&](Cursor &c) {
+            if (++c.tap == g.K) {
+                c.tap = 0;
+                ++c.cc;
+                settle(c);
+            }
+        };
+        Cursor cur_c{0, 0, 0, 0}, fetch_c{0, 0, 0, 0};
+        settle(cur_c);
+        settle(fetch_c);
+        auto coords_at = [&](const Cursor &c) {
             RawCoords<DIM> rc;
-            const int ogi = g.og > 0 ? chan0 / g.cs_per_og : 0;
-            const int mgi = g.mg > 0 ? chan0 / g.cs_per_mg : 0;
 #pragma unroll
             for (int a = 0; a < DIM; ++a)
-                rc.off[a] = off_base != nullptr ? __ldg(off_base + (int64_t)((ogi * g.K + tap) * DIM + a) * g.P) : 0.f;
-            rc.m = mask_base != nullptr ? __ldg(mask_base + (int64_t)(mgi * g.K + tap) * g.P) : 1.f;
+                rc.off[a] = off_base != nullptr ? __ldg(off_base + (int64_t)((c.ogi * g.K + c.tap) * DIM + a) * g.P) : 0.f;
+            rc.m = mask_base != nullptr ? __ldg(mask_base + (int64_t)(c.mgi * g.K + c.tap) * g.P) : 1.f;
             return rc;
         };
-        RawCoords<DIM> rc0, rc1, rc2;
-        if (n_chunks > 0) rc0 = coords_of(0);
-        if (n_chunks > 1) rc1 = coords_of(1);
-        for (int j = 0; j < n_chunks; ++j) {
+        // Plans chunk j from `cur` and requests the coordinates of chunk j + 2 into `fill`.  The three coordinate
+        // sets rotate by name (the loop below is unrolled by three), never by assignment: copying a set whose loads
+        // are still in flight would wait for them and put their latency back on the critical path.
+        auto step = [&](int j, const RawCoords<DIM> &cur, RawCoords<DIM> &fill) -> bool {
             const int pbuf = j % PLAN_BUFS;
-            const int tap = chunk_tap(j), chan0 = chunk_chan0(j);
-            if (j + 2 < n_chunks) rc2 = coords_of(j + 2);
-            const RawCoords<DIM> rc = rc0;
-            rc0 = rc1;
-            rc1 = rc2;
+            const int tap = cur_c.tap, chan0 = grp * g.csg + cur_c.cc * CHUNK_C;
+            if (j + 2 < n_chunks) {
+                fill = coords_at(fetch_c);
+                advance(fetch_c);
+            }
+            advance(cur_c);
+            if (t == 0) mark(7, j);
             bool ok = ptx::mbar_wait(&plan_empty[pbuf], (uint32_t)(((j / PLAN_BUFS) & 1) ^ 1));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 if (lane == 0) atomicExch(P.status, 106);
-                break;
+                return false;
             }
             PlanEntry *slot = plan + (pbuf * TILE_POS + t) * NC;
             int tc[DIM];
 #pragma unroll
             for (int a = 0; a < DIM; ++a) tc[a] = tap_tab[tap * DIM + a];
-            build_plan_at<DIM, MODE>(g, pi, rc, deformable, tc, row_scale, slot);
-            const uint4 *row0 = img16 + (uint32_t)chan0 * ESZ / 16u;
+            build_plan_at<DIM, MODE>(g, pi, cur, deformable, tc, row_scale, slot);
+            if (P.prefetch) {
+                const uint4 *row0 = img16 + (uint32_t)chan0 * ESZ / 16u;
 #pragma unroll
-            for (int c = 0; c < NC; ++c) {
-                if (P.prefetch && slot[c].w != 0u) {
-                    const uint4 *ptr = row0 + slot[c].row16;
-                    asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr));
-                    if (SPLIT) asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr + 8));
+                for (int c = 0; c < NC; ++c) {
+                    if (slot[c].w != 0u) {
+                        const uint4 *ptr = row0 + slot[c].row16;
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr));
+                        if (SPLIT) asm volatile("prefetch.global.L1 [%0];" ::"l"(ptr + 8));
+                    }
                 }
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&plan_full[pbuf]);
+            if (t == 0) mark(0, j);
+            return true;
+        };
+        RawCoords<DIM> r0, r1, r2;
+        if (n_chunks > 0) {
+            r0 = coords_at(fetch_c);
+            advance(fetch_c);
         }
+        if (n_chunks > 1) {
+            r1 = coords_at(fetch_c);
+            advance(fetch_c);
+        }
+        int j = 0;
+        bool ok = true;
+        for (; ok && j + 2 < n_chunks; j += 3) ok = step(j, r0, r2) && step(j + 1, r1, r0) && step(j + 2, r2, r1);
+        if (ok && j < n_chunks) ok = step(j, r0, r2);
+        if (ok && j + 1 < n_chunks) ok = step(j + 1, r1, r0);
     }
 
     ptx::tc_fence_before();
@@ -633,6 +682,15 @@ static long long *fwd_prof_buffer() {
     return (long long *)addr;
 }
 
+// Per-chunk event times of the middle CTA, filled when TVDCN_B200_PROF is 2 (tuning aid).
+__device__ long long g_fwd_trace[8 * 64];
+static long long *fwd_trace_buffer() {
+    if (tuning_int("TVDCN_B200_PROF", 0) < 2) return nullptr;
+    void *addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_fwd_trace) != cudaSuccess) return nullptr;
+    return (long long *)addr;
+}
+
 // ---- launcher -----------------------------------------------------------------------------------------
 size_t fwd_tc_smem_bytes(int dim, int mode, int bn, int stages) {
     const int parts = mode == TC_SPLIT ? 2 : 1;
@@ -681,6 +739,20 @@ cudaError_t launch_fwd_tc_t(const GeoHost &h, const FwdParams<DIM> &P, const CUt
                             "loop %lld epilogue %lld | mma wait_a %lld wait_b %lld (cycles, middle CTA)\n", h[4], h[3], h[0],
                     h[1], h[2], h[5], h[6], h[8], h[9]);
     }
+    if (P.trace != nullptr) {
+        static long long tr[8 * 64];
+        cudaStreamSynchronize(stream);
+        if (cudaMemcpy(tr, P.trace, sizeof(tr), cudaMemcpyDeviceToHost) == cudaSuccess) {
+            const int n = (int)std::min<long long>(40, (long long)h.K * P.chunks_per_tap);
+            const long long t00 = tr[7 * 64];
+            fprintf(stderr, "[dcn_fwd_tc trace] chunk: planner(wait_empty done) | producer(wait_plan start done) | "
+                            "mma(start issued) | tma issued   (cycles since the planner's first wait)\n");
+            for (int j = 0; j < n; ++j)
+                fprintf(stderr, "  %2d: %7lld %7lld | %7lld %7lld %7lld | %7lld %7lld | %7lld\n", j, tr[7 * 64 + j] - t00,
+                        tr[0 * 64 + j] - t00, tr[6 * 64 + j] - t00, tr[1 * 64 + j] - t00, tr[2 * 64 + j] - t00,
+                        tr[3 * 64 + j] - t00, tr[4 * 64 + j] - t00, tr[5 * 64 + j] - t00);
+        }
+    }
     return cudaGetLastError();
 }
 
@@ -715,6 +787,7 @@ cudaError_t launch_sample_gemm_tc(const GeoHost &h, int mode, const void *img_cl
         P.stages = stages;
         P.chunks_per_tap = csg / CHUNK_C;
         P.prof = fwd_prof_buffer();
+        P.trace = fwd_trace_buffer();
         P.prefetch = tuning_int("TVDCN_B200_PREFETCH", 0);
         if (mode == TC_BF16) return launch_fwd_tc_t<DIM, TC_BF16>(h, P, hi, lo, stream);
         if (mode == TC_F16) return launch_fwd_tc_t<DIM, TC_F16>(h, P, hi, lo, stream);
