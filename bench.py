@@ -351,6 +351,9 @@ class DeviceStep:
         self.p = cabi.make_problem(cfg.dim, cfg.transposed, code, self.x.shape[0], cfg.cin, cfg.cout, cfg.in_size,
                                    cfg.kernel, cfg.stride, cfg.padding, cfg.dilation, cfg.groups,
                                    cfg.offset_groups, cfg.mask_groups, None, cabi.F32)
+        # the backward call follows the forward call on the same workspace: it may reuse the staged input
+        self.p_bwd = cabi.Problem.from_buffer_copy(self.p)
+        self.p_bwd.flags = cabi.FLAG_REUSE_STAGED_INPUT
         pp = ctypes.byref(self.p)
         n = max(self.L.tvdcn_b200_forward_workspace_bytes(pp), self.L.tvdcn_b200_backward_workspace_bytes(pp), 256)
         self.ws = torch.empty(n, dtype=torch.uint8, device=device)
@@ -368,7 +371,8 @@ class DeviceStep:
                                                          vp(self.mask), st))
         cabi.check(L.tvdcn_b200_deform_conv_forward(pp, vp(self.x), vp(self.w), vp(self.off), vp(self.mask),
                                                     vp(self.bias), vp(self.out), vp(self.ws), self.ws.numel(), st))
-        cabi.check(L.tvdcn_b200_deform_conv_backward(pp, vp(self.go), vp(self.x), vp(self.w), vp(self.off),
+        cabi.check(L.tvdcn_b200_deform_conv_backward(ctypes.byref(self.p_bwd), vp(self.go), vp(self.x), vp(self.w),
+                                                     vp(self.off),
                                                      vp(self.mask), vp(self.gx), vp(self.gw), vp(self.goff),
                                                      vp(self.gmask), vp(self.gb), vp(self.ws), self.ws.numel(), st))
         if self.gw16 is not None:

@@ -84,7 +84,18 @@ typedef struct tvdcn_problem {
     int32_t offset_groups;     /* 0: no offset tensor (integer-grid sampling) */
     int32_t mask_groups;       /* 0: no mask tensor (factor 1)                */
     int32_t engine;            /* tvdcn_engine */
+    int32_t flags;             /* TVDCN_FLAG_* bits, 0 by default */
 } tvdcn_problem;
+
+/*
+ * Backward only, deform_conv (not transposed): the workspace passed to this backward call is the one the forward
+ * call for the same problem and the same `input` tensor ran with last, and nothing has written to it or to `input`
+ * since.  The backward call then reuses the forward call's channels-last staging of `input` (it sits at the start of
+ * both workspaces) instead of staging it again.  (No counterpart in the reference, which re-reads its inputs.)
+ * The caller vouches for all of that; with the flag clear the backward call stages the input itself.
+ * Ignored where no staging exists (SIMT kernels, transposed operator).
+ */
+#define TVDCN_FLAG_REUSE_STAGED_INPUT 1
 
 /* Validates the description and computes out_size:
  *   conv        (in + 2p - (d(k-1)+1)) / s + 1     tvdcn/csrc/ops/cuda/deform_conv2d_kernel.cpp:167-168

@@ -135,3 +135,39 @@ def test_non_finite_pixel_does_not_leak_through_out_of_image_corners(dtype):
         scale = float(r[fin].abs().max())
         err = float((a[fin] - r[fin]).abs().max()) / max(scale, 1e-30)
         assert err <= tol, f'{name}: {err:.3e}'
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16], ids=['f32split', 'bf16'])
+def test_backward_reuses_the_forward_staging(dtype):
+    """TVDCN_FLAG_REUSE_STAGED_INPUT: a backward call on the forward call's workspace gives the same gradients as
+    one that stages the input itself, with one launch less."""
+    from tvdcn_b200 import cabi
+    L = cabi.lib()
+    case = Case('reuse', 2, False, 3, 128, 64, (9, 10), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 2, 1, True, 1.5)
+    x, w, off, mask, bias, go = (None if t is None else t.cuda() for t in make_inputs(case, seed=5, dtype=torch.float32))
+    x, w, go = x.to(dtype), w.to(dtype), go.to(dtype)
+    p = cases.cabi_problem(case, dtype, torch.float32, cabi.ENGINE_TENSOR)
+    q = cabi.Problem.from_buffer_copy(p)
+    q.flags = cabi.FLAG_REUSE_STAGED_INPUT
+    n = max(L.tvdcn_b200_forward_workspace_bytes(ctypes.byref(p)), L.tvdcn_b200_backward_workspace_bytes(ctypes.byref(p)))
+    ws = torch.empty(n, dtype=torch.uint8, device='cuda')
+    vp = lambda t: ctypes.c_void_p(t.data_ptr())
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    out = torch.empty(case.batch, case.out_channels, *case.out_size, dtype=dtype, device='cuda')
+
+    def backward(prob):
+        g = [torch.full_like(t, float('nan')) for t in (x, w, off, mask, bias)]
+        cabi.check(L.tvdcn_b200_deform_conv_backward(ctypes.byref(prob), vp(go), vp(x), vp(w), vp(off), vp(mask),
+                                                     vp(g[0]), vp(g[1]), vp(g[2]), vp(g[3]), vp(g[4]), vp(ws), n, st))
+        return g
+
+    base = backward(p)                       # stages the input itself
+    ws.fill_(0xff)                           # nothing useful left in the workspace
+    cabi.check(L.tvdcn_b200_deform_conv_forward(ctypes.byref(p), vp(x), vp(w), vp(off), vp(mask), vp(bias), vp(out),
+                                                vp(ws), n, st))
+    names, got = kernels_launched(lambda: backward(q))
+    assert names.get('to_channels_last', 0) == 1, names       # grad_output only; the input staging was reused
+    for a, b in zip(got, base):
+        assert torch.isfinite(a.float()).all()
+        assert nerr(a, b) < 1e-5
+    assert L.tvdcn_b200_device_status() == 0

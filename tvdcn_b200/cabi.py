@@ -13,6 +13,7 @@ from .extension import c_abi
 
 F32, F64, F16, BF16 = 0, 1, 2, 3
 ENGINE_AUTO, ENGINE_SIMT, ENGINE_TENSOR = 0, 1, 2
+FLAG_REUSE_STAGED_INPUT = 1   # backward: the workspace still holds the forward call's staging of `input`
 
 
 class Problem(C.Structure):
@@ -24,6 +25,7 @@ class Problem(C.Structure):
         ('kernel', C.c_int32 * 3), ('stride', C.c_int32 * 3), ('padding', C.c_int32 * 3),
         ('dilation', C.c_int32 * 3), ('output_padding', C.c_int32 * 3),
         ('groups', C.c_int32), ('offset_groups', C.c_int32), ('mask_groups', C.c_int32), ('engine', C.c_int32),
+        ('flags', C.c_int32),
     ]
 
 

@@ -68,6 +68,7 @@ int check_problem(const tvdcn_problem *p) {
     if (p == nullptr) return fail(TVDCN_ERR_INVALID, "problem is NULL");
     if (p->dim < 1 || p->dim > 3) return fail(TVDCN_ERR_INVALID, "dim must be 1, 2 or 3 (got %d)", p->dim);
     if (p->dtype < TVDCN_F32 || p->dtype > TVDCN_BF16) return fail(TVDCN_ERR_INVALID, "unknown dtype %d", p->dtype);
+    if ((p->flags & ~TVDCN_FLAG_REUSE_STAGED_INPUT) != 0) return fail(TVDCN_ERR_INVALID, "unknown flags 0x%x", p->flags);
     const bool aux_ok = p->aux_dtype == p->dtype ||
                         (p->aux_dtype == TVDCN_F32 && (p->dtype == TVDCN_F16 || p->dtype == TVDCN_BF16));
     if (!aux_ok)
@@ -426,7 +427,13 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
     rc = check_ws(pl, workspace, workspace_bytes);
     if (rc) return rc;
     char *ws = (char *)workspace;
+    // the caller may vouch that the forward call's staging of `input` is still at the start of this workspace
+    // (only where the forward call for this problem stages the image at all, and at the same offset)
     t_staged_image = nullptr;
+    if ((p->flags & TVDCN_FLAG_REUSE_STAGED_INPUT) && !p->transposed && pl.tensor) {
+        const Plan fwd = plan_forward(p);
+        if (fwd.img_cl != NO_BUF && fwd.img_cl == pl.img_cl) t_staged_image = input;
+    }
 
     const size_t acs = dtype_size(acc_dtype(dt));
     // accumulation targets: the outputs themselves when they already have the accumulation type

@@ -105,28 +105,28 @@ Plan plan_backward(const tvdcn_problem *p, bool want_input, bool want_weight, bo
     want_mask = want_mask && g.mg > 0;
     if (why == nullptr) {
         int bn = 0, st = 0, ns = 0, mt = 0, gbufs = 0;
+        // which primitives run on the tensor cores
         // transposed backward: grad_input is a sample -> GEMM over grad_output
-        if (p->transposed && want_input && fwd_tc_config(g.dim, mode, g.Cd / g.groups, &bn, &st) &&
-            chain_ok(mode, g, bn)) {
-            pl.tc_sg = true;
+        pl.tc_sg = p->transposed && want_input && fwd_tc_config(g.dim, mode, g.Cd / g.groups, &bn, &st) &&
+                   chain_ok(mode, g, bn);
+        pl.tc_sw = want_weight && wgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.P, &ns, &mt, &st);
+        // conv: scatter into grad_input + coordinate gradients; transposed: coordinate gradients only
+        const bool scatter = !p->transposed && want_input;
+        pl.tc_gs = (scatter || want_offset || want_mask) &&
+                   dgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.Cs / g.groups, &bn, &st, &gbufs);
+        pl.tensor = pl.tc_sg || pl.tc_sw || pl.tc_gs;
+        // The staged image comes first, as in the forward plan: a backward call that is told to reuse the
+        // forward call's staging (TVDCN_FLAG_REUSE_STAGED_INPUT) finds it at the same offset of the same workspace.
+        if (pl.tensor) pl.img_cl = b.take(((size_t)g.B * g.S + 1) * g.Cs * es);
+        if (pl.tc_sg) {
             pl.w_pack = b.take(nw * 2);
             if (p->dtype == TVDCN_F32) pl.w_pack_lo = b.take(nw * 2);
         }
-        if (want_weight && wgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.P, &ns, &mt, &st)) {
-            pl.tc_sw = true;
-            if (p->dtype == TVDCN_F32) {
-                pl.dense_hi = b.take((size_t)g.B * g.Cd * g.P * 2);
-                pl.dense_lo = b.take((size_t)g.B * g.Cd * g.P * 2);
-            }
+        if (pl.tc_sw && p->dtype == TVDCN_F32) {
+            pl.dense_hi = b.take((size_t)g.B * g.Cd * g.P * 2);
+            pl.dense_lo = b.take((size_t)g.B * g.Cd * g.P * 2);
         }
-        // conv: scatter into grad_input + coordinate gradients; transposed: coordinate gradients only
-        const bool scatter = !p->transposed && want_input;
-        if ((scatter || want_offset || want_mask) && dgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.Cs / g.groups, &bn, &st, &gbufs)) {
-            pl.tc_gs = true;
-            take_scatter_buffers(pl, b, p, g, scatter);
-        }
-        pl.tensor = pl.tc_sg || pl.tc_sw || pl.tc_gs;
-        if (pl.tensor) pl.img_cl = b.take(((size_t)g.B * g.S + 1) * g.Cs * es);
+        if (pl.tc_gs) take_scatter_buffers(pl, b, p, g, scatter);
         if (!pl.tensor) pl.why_not = "no tensor-core kernel covers the requested gradients for this shape";
     } else {
         pl.why_not = why;
