@@ -167,7 +167,9 @@ def test_backward_reuses_the_forward_staging(dtype):
                                                 vp(ws), n, st))
     names, got = kernels_launched(lambda: backward(q))
     assert names.get('to_channels_last', 0) == 1, names       # grad_output only; the input staging was reused
+    # same arithmetic, but the f32 atomics land in another order: a bf16 result may round the other way
+    tol = 1e-5 if dtype == torch.float32 else 4e-3
     for a, b in zip(got, base):
         assert torch.isfinite(a.float()).all()
-        assert nerr(a, b) < 1e-5
+        assert nerr(a, b) < tol
     assert L.tvdcn_b200_device_status() == 0
