@@ -63,7 +63,7 @@ cudaError_t launch_gemm_scatter_tc(const GeoHost &g, int mode, const void *dense
                                    const float *mask, float *img_grad_cl, float *goff, float *gmask, int *status,
                                    cudaStream_t stream);
 cudaError_t launch_to_channels_last_split(const float *src, void *hi, void *lo, int B, int C, int S,
-                                          cudaStream_t stream);
+                                          cudaStream_t stream, void *hi_same = nullptr, void *lo_same = nullptr);
 cudaError_t launch_from_channels_last_bias(const float *src, const float *bias, void *dst, int dst_dtype, int B, int C,
                                            int S, cudaStream_t stream);
 cudaError_t launch_pack_weight_kd(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,

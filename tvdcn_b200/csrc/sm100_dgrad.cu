@@ -768,7 +768,9 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
 // [B, C, S] f32 -> [B, S, C] bf16 hi + lo
 __global__ void __launch_bounds__(256) to_channels_last_split_kernel(const float *__restrict__ src,
                                                                      __nv_bfloat16 *__restrict__ hi,
-                                                                     __nv_bfloat16 *__restrict__ lo, int C, int S) {
+                                                                     __nv_bfloat16 *__restrict__ lo, int C, int S,
+                                                                     __nv_bfloat16 *__restrict__ hi_same,
+                                                                     __nv_bfloat16 *__restrict__ lo_same) {
     __shared__ float tile[32][33];
     const int b = blockIdx.z;
     const int s0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
@@ -777,7 +779,16 @@ __global__ void __launch_bounds__(256) to_channels_last_split_kernel(const float
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
         const int c = c0 + ty + 8 * i, s = s0 + tx;
-        if (c < C && s < S) tile[ty + 8 * i][tx] = in[(int64_t)c * S + s];
+        if (c < C && s < S) {
+            const float v = in[(int64_t)c * S + s];
+            tile[ty + 8 * i][tx] = v;
+            if (hi_same != nullptr) {
+                const __nv_bfloat16 h = __float2bfloat16_rn(v);
+                const int64_t o = (int64_t)b * C * S + (int64_t)c * S + s;
+                hi_same[o] = h;
+                lo_same[o] = __float2bfloat16_rn(v - __bfloat162float(h));
+            }
+        }
     }
     __syncthreads();
 #pragma unroll
@@ -798,7 +809,9 @@ __global__ void __launch_bounds__(256) to_channels_last_split_kernel(const float
 // transposing reads of a channel pair per lane are free of bank conflicts.
 __global__ void __launch_bounds__(256) to_channels_last_split64_kernel(const float *__restrict__ src,
                                                                        uint32_t *__restrict__ hi,
-                                                                       uint32_t *__restrict__ lo, int C, int S) {
+                                                                       uint32_t *__restrict__ lo, int C, int S,
+                                                                       uint2 *__restrict__ hi_same,
+                                                                       uint2 *__restrict__ lo_same) {
     __shared__ float tile[64 * 65];
     const int b = blockIdx.z;
     const int s0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
@@ -809,7 +822,22 @@ __global__ void __launch_bounds__(256) to_channels_last_split64_kernel(const flo
         const int cl = pass * 16 + r;
         const int c = c0 + cl, s = s0 + v * 4;
         float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (c < C && s < S) x = __ldg(reinterpret_cast<const float4 *>(in + (int64_t)c * S + s));
+        if (c < C && s < S) {
+            x = __ldg(reinterpret_cast<const float4 *>(in + (int64_t)c * S + s));
+            if (hi_same != nullptr) {   // the same split in the source layout, while the values are in registers
+                const float f[4] = {x.x, x.y, x.z, x.w};
+                uint32_t h[4], l[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const __nv_bfloat16 hb = __float2bfloat16_rn(f[k]);
+                    h[k] = __bfloat16_as_ushort(hb);
+                    l[k] = __bfloat16_as_ushort(__float2bfloat16_rn(f[k] - __bfloat162float(hb)));
+                }
+                const int64_t o = ((int64_t)b * C * S + (int64_t)c * S + s) >> 2;
+                hi_same[o] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+                lo_same[o] = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+            }
+        }
         float *w = tile + ((cl >> 1) + 32 * (cl & 1)) * 65 + v * 4;
         w[0] = x.x;
         w[1] = x.y;
@@ -946,16 +974,21 @@ bool dgrad_tc_config(int dim, int mode, int cdg, int csg, int *nb, int *b_stages
     return false;
 }
 
+// hi_same / lo_same (both or neither): the same hi + lo split in the layout of the source, written in the same pass
 cudaError_t launch_to_channels_last_split(const float *src, void *hi, void *lo, int B, int C, int S,
-                                          cudaStream_t stream) {
+                                          cudaStream_t stream, void *hi_same, void *lo_same) {
     dim3 grid((S + 31) / 32, (C + 31) / 32, B);
     LaunchScope scope("to_channels_last", stream);
-    if (S % 4 == 0 && C % 2 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+    const bool same_ok = hi_same == nullptr ||
+                         ((reinterpret_cast<uintptr_t>(hi_same) | reinterpret_cast<uintptr_t>(lo_same)) & 7) == 0;
+    if (S % 4 == 0 && C % 2 == 0 && same_ok && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
         ((reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(lo)) & 3) == 0) {
         dim3 grid64((S + 63) / 64, (C + 63) / 64, B);
-        to_channels_last_split64_kernel<<<grid64, 256, 0, stream>>>(src, (uint32_t *)hi, (uint32_t *)lo, C, S);
+        to_channels_last_split64_kernel<<<grid64, 256, 0, stream>>>(src, (uint32_t *)hi, (uint32_t *)lo, C, S,
+                                                                   (uint2 *)hi_same, (uint2 *)lo_same);
     } else {
-        to_channels_last_split_kernel<<<grid, 256, 0, stream>>>(src, (__nv_bfloat16 *)hi, (__nv_bfloat16 *)lo, C, S);
+        to_channels_last_split_kernel<<<grid, 256, 0, stream>>>(src, (__nv_bfloat16 *)hi, (__nv_bfloat16 *)lo, C, S,
+                                                                (__nv_bfloat16 *)hi_same, (__nv_bfloat16 *)lo_same);
     }
     return cudaGetLastError();
 }
