@@ -311,9 +311,9 @@ def known_traffic(kernel: str, config: int, mode: str):
     """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
     under profiles/ (config2_tensor_kernels.md); None where no capture exists."""
     table = {
-        'dcn_fwd_tc/cfg2/bf16': 85.14e6 + 22.25e6,
-        'dcn_dgrad_tc/cfg2/bf16': 272.38e6 + 90.03e6,
-        'dcn_wgrad_tc/cfg2/bf16': 137.70e6 + 3.46e6,
+        'dcn_fwd_tc/cfg2/bf16': 85.16e6 + 21.68e6,
+        'dcn_dgrad_tc/cfg2/bf16': 329.76e6 + 104.70e6,
+        'dcn_wgrad_tc/cfg2/bf16': 137.71e6 + 3.80e6,
         'dcn_fwd_tc/cfg2/fp32': 137.83e6 + 68.71e6,
         'dcn_dgrad_tc/cfg2/fp32': 377.43e6 + 104.86e6,
         'dcn_wgrad_tc/cfg2/fp32': 245.56e6 + 9.95e6,
