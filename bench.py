@@ -314,9 +314,9 @@ def known_traffic(kernel: str, config: int, mode: str):
         'dcn_fwd_tc/cfg2/bf16': 85.16e6 + 21.68e6,
         'dcn_dgrad_tc/cfg2/bf16': 329.76e6 + 104.70e6,
         'dcn_wgrad_tc/cfg2/bf16': 137.71e6 + 3.80e6,
-        'dcn_fwd_tc/cfg2/fp32': 137.83e6 + 68.71e6,
-        'dcn_dgrad_tc/cfg2/fp32': 377.43e6 + 104.86e6,
-        'dcn_wgrad_tc/cfg2/fp32': 245.56e6 + 9.95e6,
+        'dcn_fwd_tc/cfg2/fp32': 138.19e6 + 65.25e6,
+        'dcn_dgrad_tc/cfg2/fp32': 485.68e6 + 115.06e6,
+        'dcn_wgrad_tc/cfg2/fp32': 245.74e6 + 7.91e6,
     }
     return table.get(f'{kernel}/cfg{config}/{mode}')
 
