@@ -156,9 +156,6 @@ int *device_status_word() {
 // The channels-last copy of the sampled image is shared by every tensor-core kernel of one call; the entry
 // points reset this marker, the first user stages the image.
 static thread_local const void *t_staged_image = nullptr;
-// f32 data: the dense tensor whose bf16 hi + lo splits (channels-last for the scatter kernel, source layout for the
-// weight-gradient kernel) the backward entry point has already made in one pass; reset by the entry points.
-static thread_local const void *t_split_dense = nullptr;
 
 static cudaError_t stage_image(const tvdcn_problem *p, const GeoHost &g, const Plan &pl, const void *img, char *ws,
                                cudaStream_t stream) {
@@ -202,19 +199,9 @@ static cudaError_t run_gemm_scatter_tc(const tvdcn_problem *p, const GeoHost &g,
     const int mode = tc_mode_of(p->dtype);
     int *status = device_status_word();
     if (status == nullptr) return cudaErrorInvalidDevice;
-    void *d_hi = ws + pl.dense_cl;
-    void *d_lo = pl.dense_cl_lo != NO_BUF ? (void *)(ws + pl.dense_cl_lo) : nullptr;
     void *w_hi = ws + pl.w_pack_kd;
     void *w_lo = pl.w_pack_kd_lo != NO_BUF ? (void *)(ws + pl.w_pack_kd_lo) : nullptr;
-    cudaError_t e;
-    if (p->dtype == TVDCN_F32)
-        e = t_split_dense == dense
-                ? cudaSuccess
-                : launch_to_channels_last_split((const float *)dense, d_hi, d_lo, g.B, g.Cd, g.P, stream);
-    else
-        e = launch_to_channels_last(dense, d_hi, g.B, g.Cd, g.P, 2, stream);
-    if (e != cudaSuccess) return e;
-    e = launch_pack_weight_kd(weight, p->dtype, mode, g.groups, g.Cd / g.groups, g.Cs / g.groups, g.K, w_hi, w_lo,
+    cudaError_t e = launch_pack_weight_kd(weight, p->dtype, mode, g.groups, g.Cd / g.groups, g.Cs / g.groups, g.K, w_hi, w_lo,
                               stream);
     if (e != cudaSuccess) return e;
     const bool want_coord = goff != nullptr || gmask != nullptr;
@@ -228,7 +215,7 @@ static cudaError_t run_gemm_scatter_tc(const tvdcn_problem *p, const GeoHost &g,
         e = cudaMemsetAsync(acc, 0, (size_t)g.B * g.S * g.Cs * sizeof(float), stream);
         if (e != cudaSuccess) return e;
     }
-    e = launch_gemm_scatter_tc(g, mode, d_hi, d_lo, w_hi, w_lo, want_coord ? ws + pl.img_cl : nullptr,
+    e = launch_gemm_scatter_tc(g, mode, dense, w_hi, w_lo, want_coord ? ws + pl.img_cl : nullptr,
                                (const float *)offset, (const float *)mask, acc, (float *)goff, (float *)gmask, status,
                                stream);
     if (e != cudaSuccess) return e;
@@ -248,8 +235,7 @@ static cudaError_t run_sample_wgrad_tc(const tvdcn_problem *p, const GeoHost &g,
     if (e != cudaSuccess) return e;
     const void *d_hi = dense, *d_lo = nullptr;
     if (p->dtype == TVDCN_F32) {
-        if (t_split_dense != dense)
-            e = launch_split_f32((const float *)dense, ws + pl.dense_hi, ws + pl.dense_lo, (int64_t)g.B * g.Cd * g.P,
+        e = launch_split_f32((const float *)dense, ws + pl.dense_hi, ws + pl.dense_lo, (int64_t)g.B * g.Cd * g.P,
                                  stream);
         if (e != cudaSuccess) return e;
         d_hi = ws + pl.dense_hi;
@@ -336,7 +322,6 @@ int tvdcn_b200_deform_conv_forward(const tvdcn_problem *p, const void *input, co
     if (rc) return rc;
     char *ws = (char *)workspace;
     t_staged_image = nullptr;
-    t_split_dense = nullptr;
     const GeoHost g = make_geo_host(p);
     const int dt = p->dtype, aux = p->aux_dtype;
 
@@ -450,16 +435,6 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
     if (gw_acc) CUDA_TRY(cudaMemsetAsync(gw_acc, 0, n_w * acs, stream));
     if (goff_acc) CUDA_TRY(cudaMemsetAsync(goff_acc, 0, n_off * acs, stream));
     if (gmask_acc) CUDA_TRY(cudaMemsetAsync(gmask_acc, 0, n_mask * acs, stream));
-
-    // f32 data, scatter and weight-gradient kernels both on the tensor cores: both want the dense tensor as bf16
-    // hi + lo, one channels-last, one in the source layout; one pass over it makes both
-    t_split_dense = nullptr;
-    if (p->dtype == TVDCN_F32 && pl.tc_gs && pl.tc_sw && gw_acc) {
-        const void *dense = p->transposed ? input : grad_output;
-        CUDA_TRY(launch_to_channels_last_split((const float *)dense, ws + pl.dense_cl, ws + pl.dense_cl_lo, g.B, g.Cd,
-                                               g.P, stream, ws + pl.dense_hi, ws + pl.dense_lo));
-        t_split_dense = dense;
-    }
 
     // fork: weight gradient + bias sum on the side stream when both sides run on the tensor cores
     SideStream *side = (pl.tc_sw && gw_acc && (pl.tc_gs || pl.tc_sg)) ? side_stream() : nullptr;

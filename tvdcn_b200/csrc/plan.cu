@@ -46,13 +46,8 @@ bool chain_ok(int mode, const GeoHost &g, int bn) {
 // buffers of the GEMM -> scatter kernel
 void take_scatter_buffers(Plan &pl, Bump &b, const tvdcn_problem *p, const GeoHost &g, bool scatter) {
     const size_t nw = (size_t)g.Cd * (g.Cs / g.groups) * g.K;
-    const size_t nd = (size_t)g.B * g.Cd * g.P;
-    pl.dense_cl = b.take(nd * 2);
     pl.w_pack_kd = b.take(nw * 2);
-    if (p->dtype == TVDCN_F32) {
-        pl.dense_cl_lo = b.take(nd * 2);
-        pl.w_pack_kd_lo = b.take(nw * 2);
-    }
+    if (p->dtype == TVDCN_F32) pl.w_pack_kd_lo = b.take(nw * 2);
     if (scatter) pl.img_grad_cl = b.take((size_t)g.B * g.S * g.Cs * sizeof(float));
 }
 }  // namespace
@@ -78,7 +73,7 @@ Plan plan_forward(const tvdcn_problem *p) {
             why = "no tile configuration fits (or the f32 accumulation chain would be too long)";
         }
     } else if (why == nullptr) {
-        if (dgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.Cs / g.groups, &bn, &st, &gbufs)) {
+        if (dgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.K, &bn, &gbufs, &st)) {
             pl.tensor = pl.tc_gs = true;
             take_scatter_buffers(pl, b, p, g, true);
         } else {
@@ -113,7 +108,7 @@ Plan plan_backward(const tvdcn_problem *p, bool want_input, bool want_weight, bo
         // conv: scatter into grad_input + coordinate gradients; transposed: coordinate gradients only
         const bool scatter = !p->transposed && want_input;
         pl.tc_gs = (scatter || want_offset || want_mask) &&
-                   dgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.Cs / g.groups, &bn, &st, &gbufs);
+                   dgrad_tc_config(g.dim, mode, g.Cd / g.groups, g.K, &bn, &gbufs, &st);
         pl.tensor = pl.tc_sg || pl.tc_sw || pl.tc_gs;
         // The staged image comes first, as in the forward plan: a backward call that is told to reuse the
         // forward call's staging (TVDCN_FLAG_REUSE_STAGED_INPUT) finds it at the same offset of the same workspace.

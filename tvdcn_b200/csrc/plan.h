@@ -29,8 +29,6 @@ struct Plan {
     size_t w_pack_lo = NO_BUF;     // low part of the split
     size_t w_pack_kd = NO_BUF;     // weights packed [g][tap][s'][d']
     size_t w_pack_kd_lo = NO_BUF;
-    size_t dense_cl = NO_BUF;      // dense tensor, channels-last 16-bit (hi)
-    size_t dense_cl_lo = NO_BUF;
     size_t dense_hi = NO_BUF;      // dense tensor, original layout, 16-bit hi / lo (split mode)
     size_t dense_lo = NO_BUF;
     size_t img_grad_cl = NO_BUF;   // f32 channels-last accumulator of the scatter
@@ -57,13 +55,10 @@ bool wgrad_tc_config(int dim, int mode, int cdg, int P, int *n_sub, int *m_tiles
 cudaError_t launch_sample_wgrad_tc(const GeoHost &g, int mode, const void *dense_hi, const void *dense_lo,
                                    const void *img_cl, const float *offset, const float *mask, float *gw,
                                    int *status, cudaStream_t stream);
-bool dgrad_tc_config(int dim, int mode, int cdg, int csg, int *nb, int *b_stages, int *g_bufs);
-cudaError_t launch_gemm_scatter_tc(const GeoHost &g, int mode, const void *dense_cl_hi, const void *dense_cl_lo,
-                                   const void *w_kd_hi, const void *w_kd_lo, const void *img_cl, const float *offset,
-                                   const float *mask, float *img_grad_cl, float *goff, float *gmask, int *status,
-                                   cudaStream_t stream);
-cudaError_t launch_to_channels_last_split(const float *src, void *hi, void *lo, int B, int C, int S,
-                                          cudaStream_t stream, void *hi_same = nullptr, void *lo_same = nullptr);
+bool dgrad_tc_config(int dim, int mode, int cdg, int K, int *tb, int *nacc, int *b_stages);
+cudaError_t launch_gemm_scatter_tc(const GeoHost &g, int mode, const void *dense, const void *w_kd_hi,
+                                   const void *w_kd_lo, const void *img_cl, const float *offset, const float *mask,
+                                   float *img_grad_cl, float *goff, float *gmask, int *status, cudaStream_t stream);
 cudaError_t launch_from_channels_last_bias(const float *src, const float *bias, void *dst, int dst_dtype, int B, int C,
                                            int S, cudaStream_t stream);
 cudaError_t launch_pack_weight_kd(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
