@@ -45,6 +45,9 @@ def build_cuda_library(verbose: bool = False, force: bool = False) -> Path:
     headers = sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.cuh")) + sorted(INCLUDE.glob("*.h"))
     OBJ.mkdir(exist_ok=True)
     flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if verbose else [])
+    if os.environ.get("TVDCN_B200_TUNING"):      # in-kernel cycle counters, never part of a normal build
+        flags.append("-DTVDCN_B200_TUNING")
+    flags += os.environ.get("TVDCN_B200_NVCC_FLAGS", "").split()   # extra flags for experiments
     jobs = []
     for src in cu:
         obj = OBJ / (src.stem + ".o")

@@ -27,6 +27,15 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// ---- registers ----------------------------------------------------------------------------------
+// Moves registers between the warpgroups (4 consecutive warps, all of which must execute the instruction) of a
+// warp-specialised CTA: the roles that only issue copies or MMAs give registers up, the roles with real loops take
+// them.  An increase waits until the pool holds enough; the totals must therefore balance (see the kernel).
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // ---- mbarrier -----------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -66,10 +75,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
 }
 // Same bound, with a short sleep between polls: the waiting warp gives its issue slots to the warps that share its
 // scheduler, at the price of a later wake-up.  Pays where the waiters outnumber the workers (measured per kernel).
+template <int NS = 32>
 __device__ __forceinline__ bool mbar_wait_backoff(uint64_t *bar, uint32_t parity) {
     for (uint32_t i = 0; i < kMaxPolls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(32);
+        __nanosleep(NS);
     }
     return false;
 }
@@ -144,6 +154,17 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
         "}\n"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The same with the accumulate flag fixed to "add into D": no predicate to set up per instruction.
+__device__ __forceinline__ void mma_f16_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
         : "memory");
 }
 // Arrives on the mbarrier once every MMA issued so far by this thread has completed.
