@@ -75,6 +75,7 @@ static_assert(SC_THREADS == 768, "six warpgroups");
 constexpr int SC_REGS_WORK = 96, SC_REGS_STORE = 56, SC_REGS_ISSUE = 40;
 constexpr int SC_GROUPS = SC_GATHER_WARPS * 4;                    // 8-lane groups walking the entry list
 constexpr int SC_SLAB = 32;                                       // channels per pass
+constexpr int SC_PLAN_SLACK = SC_GROUPS * 5 + 16;
 constexpr int SC_HASH = 2048;                                     // slots; >= entries of one unit
 constexpr uint32_t SC_NONE = 0xffffffffu;
 constexpr int SC_TMEM_COLS = 512;
@@ -174,9 +175,10 @@ __host__ __device__ inline ScLayout sc_layout(int dim, int mode, int tb, int b_s
     L.b_stage = (uint32_t)(L.n * 128);             // one 16-bit part (hi or lo) of one reduction chunk
     (void)parts;
     L.col_buf = (uint32_t)(TILE_POS * L.col_stride * 4);
-    // entries {pixel offset, col index | dot slot << 16, weight, -} with room for the padding of the groups' spans and
-    // for the read-ahead of the last group, then one dot product per entry (+ a slot for the padding entries)
-    L.plan_buf = (uint32_t)((L.max_entries + SC_GROUPS * 4 + 16) * 16 + (L.max_entries + 4) * 4);
+    // three arrays (pixel offset; col index | dot slot << 16; weight) of max_entries + SC_PLAN_SLACK words -- room for
+    // the padding of the groups' spans, one unused word between the groups and the read-ahead of the last group --
+    // then one dot product per entry (+ a slot for the padding entries)
+    L.plan_buf = (uint32_t)(3 * (L.max_entries + SC_PLAN_SLACK) * 4 + (L.max_entries + 4) * 4);
     uint32_t o = 0;
     o += (uint32_t)b_stages * L.b_stage;
     L.col = o;  o += 2 * L.col_buf;
@@ -230,8 +232,13 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
     uint64_t *plan_done = plan_full + 2; // [2] gather warps -> whoever turns the unit's dots into gradients / planners
     uint64_t *fin_done = plan_done + 2;  // [2] store warps -> planners: the unit's dots have been used
     int16_t *tap_tab = reinterpret_cast<int16_t *>(smem + L.taps);
-    auto plan_ent = [&](int pb) { return reinterpret_cast<uint4 *>(smem + L.plan + (size_t)pb * L.plan_buf); };
-    auto plan_dot = [&](int pb) { return reinterpret_cast<float *>(plan_ent(pb) + L.max_entries + SC_GROUPS * 4 + 16); };
+    // Entry e of the pixel-grouped list sits at word e + e / span of each array: the groups' spans start span + 1
+    // words apart, so that the four groups of a gather warp read four different banks.
+    const int plan_words = L.max_entries + SC_PLAN_SLACK;
+    auto plan_px = [&](int pb) { return reinterpret_cast<uint32_t *>(smem + L.plan + (size_t)pb * L.plan_buf); };
+    auto plan_meta = [&](int pb) { return plan_px(pb) + plan_words; };
+    auto plan_w = [&](int pb) { return reinterpret_cast<float *>(plan_px(pb) + 2 * plan_words); };
+    auto plan_dot = [&](int pb) { return reinterpret_cast<float *>(plan_px(pb) + 3 * plan_words); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int grp = blockIdx.y;
@@ -537,7 +544,9 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                     break;
                 }
                 const int span = (int)n_entries[pb];     // entries per group, padded: a multiple of 4
-                const uint4 *my = plan_ent(pb) + gid * span;
+                const uint32_t *my_px = plan_px(pb) + gid * (span + 1);
+                const uint32_t *my_meta = plan_meta(pb) + gid * (span + 1);
+                const float *my_w = plan_w(pb) + gid * (span + 1);
                 float *p_dot = plan_dot(pb);
                 const float4 *colb = reinterpret_cast<const float4 *>(col + (size_t)cb * (L.col_buf / 4)) + l8;
                 const uint32_t chan = (uint32_t)(grp * g.csg + chunk * CHUNK_C + slab * SC_SLAB + l8 * 4);
@@ -546,12 +555,11 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
 
                 uint32_t cur = zrow;
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                // image rows of the four entries at `at` (only their first word, the pixel offset, is read here)
-                auto fetch_rows = [&](RAW (&R)[4], int at) {
-                    if constexpr (COORD) {
-                        uint32_t px[4];
+                // pixel offsets of the four entries at `at`, and (for the coordinate gradients) their image rows
+                auto fetch_rows = [&](uint32_t (&px)[4], RAW (&R)[4], int at) {
 #pragma unroll
-                        for (int s = 0; s < 4; ++s) px[s] = my[at + s].x;
+                    for (int s = 0; s < 4; ++s) px[s] = my_px[at + s];
+                    if constexpr (COORD) {
 #pragma unroll
                         for (int s = 0; s < 4; ++s) R[s] = __ldg(reinterpret_cast<const RAW *>(img_c + px[s]));
                     }
@@ -569,19 +577,23 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                                            __uint_as_float(r.y << 16), __uint_as_float(r.y & 0xffff0000u));
                     }
                 };
-                auto process = [&](int at, const RAW (&R)[4]) {
-                    uint4 E[4];
+                auto process = [&](int at, const uint32_t (&pxs)[4], const RAW (&R)[4]) {
+                    uint32_t meta[4];
+                    float wt[4];
 #pragma unroll
-                    for (int s = 0; s < 4; ++s) E[s] = my[at + s];
+                    for (int s = 0; s < 4; ++s) {
+                        meta[s] = my_meta[at + s];
+                        wt[s] = my_w[at + s];
+                    }
                     float d[4];
 #pragma unroll
                     for (int s = 0; s < 4; ++s) {
-                        const uint32_t px = E[s].x;
+                        const uint32_t px = pxs[s];
                         const bool change = px != cur;
                         red_add_v4_if(change && cur != zrow && scatter, gimg_c + cur, acc.x, acc.y, acc.z, acc.w);
                         cur = px;
-                        const float4 c4 = colb[E[s].y & 0xffffu];
-                        const float w = __uint_as_float(E[s].z);
+                        const float4 c4 = colb[meta[s] & 0xffffu];
+                        const float w = wt[s];
                         acc.x = fmaf(w, c4.x, change ? 0.f : acc.x);
                         acc.y = fmaf(w, c4.y, change ? 0.f : acc.y);
                         acc.z = fmaf(w, c4.z, change ? 0.f : acc.z);
@@ -602,21 +614,22 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                         k += __shfl_xor_sync(0xffffffffu, h2 ? k0 : k1, 2);
                         k += __shfl_xor_sync(0xffffffffu, k, 1);
                         if ((l8 & 1) == 0) {
-                            const uint32_t m = h4 ? (h2 ? E[3].y : E[2].y) : (h2 ? E[1].y : E[0].y);
+                            const uint32_t m = h4 ? (h2 ? meta[3] : meta[2]) : (h2 ? meta[1] : meta[0]);
                             float *slot = p_dot + (m >> 16);
                             *slot = slab == 0 ? k : *slot + k;
                         }
                     }
                 };
                 RAW Ra[4], Rb[4];
-                if (span > 0) fetch_rows(Ra, 0);
+                uint32_t Pa[4], Pb[4];
+                if (span > 0) fetch_rows(Pa, Ra, 0);
                 for (int it = 0; it < span; it += 8) {
                     // the fetch one batch ahead may run up to 8 entries past the span: still inside the list's slack
-                    fetch_rows(Rb, it + 4);
-                    process(it, Ra);
+                    fetch_rows(Pb, Rb, it + 4);
+                    process(it, Pa, Ra);
                     if (it + 4 < span) {
-                        fetch_rows(Ra, it + 8);
-                        process(it + 4, Rb);
+                        fetch_rows(Pa, Ra, it + 8);
+                        process(it + 4, Pb, Rb);
                     }
                 }
                 red_add_v4_if(cur != zrow && scatter, gimg_c + cur, acc.x, acc.y, acc.z, acc.w);
@@ -746,24 +759,34 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
             if (pt == 0) n_entries[pb] = span;
             planner_barrier();
             phase(3);
-            // pass 2: every entry goes to (start of its pixel's run) + (its rank)
-            uint4 *ent = plan_ent(pb);
-            uint32_t at[TBM * NC];
-#pragma unroll
-            for (int i = 0; i < TBM * NC; ++i) at[i] = rows[i] != SC_NONE ? cnt[slot[i]] + old[i] : 0u;
+            // pass 2: every entry goes to (start of its pixel's run) + (its rank), counted in the padded layout
+            uint32_t *e_px = plan_px(pb);
+            uint32_t *e_meta = plan_meta(pb);
+            float *e_w = plan_w(pb);
+            const uint32_t magic = span > 0 ? (uint32_t)((0x100000000ull + span - 1) / span) : 0u;   // e / span for e < 2^16
 #pragma unroll
             for (int t = 0; t < TBM; ++t) {
 #pragma unroll
                 for (int c = 0; c < NC; ++c) {
                     const int i = t * NC + c;
-                    if (rows[i] != SC_NONE)
-                        ent[at[i]] = make_uint4(rows[i] * (uint32_t)g.Cs,
-                                                (colq_row + (uint32_t)(t * (SC_SLAB / 4))) | ((uint32_t)((pt * TB + t) * NC + c) << 16),
-                                                __float_as_uint(wts[i]), 0u);
+                    if (rows[i] != SC_NONE) {
+                        const uint32_t e = cnt[slot[i]] + old[i];
+                        const uint32_t at = e + __umulhi(e, magic);
+                        e_px[at] = rows[i] * (uint32_t)g.Cs;
+                        e_meta[at] = (colq_row + (uint32_t)(t * (SC_SLAB / 4))) | ((uint32_t)((pt * TB + t) * NC + c) << 16);
+                        e_w[at] = wts[i];
+                    }
                 }
             }
-            for (uint32_t i = total + pt; i < span * SC_GROUPS + 8; i += 128)
-                ent[i] = make_uint4(zrow, (uint32_t)L.max_entries << 16, 0u, 0u);
+            // padding entries up to the end of the last span, the unused word after each span and the words the
+            // read-ahead of the last group touches: all point at the row of zeros and add nothing
+            const uint32_t n_words = span * SC_GROUPS + SC_GROUPS + 8;
+            for (uint32_t i = total + total / (span > 0 ? span : 1) + pt; i < n_words; i += 128) {
+                e_px[i] = zrow;
+                e_meta[i] = (uint32_t)L.max_entries << 16;
+                e_w[i] = 0.f;
+            }
+            if (pt < SC_GROUPS && span > 0) e_px[pt * (span + 1) + span] = zrow;
             phase(4);
             planner_barrier();
             phase(5);
