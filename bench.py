@@ -215,8 +215,8 @@ def load_reference():
     from oracle import build_ref
     if build_ref.load():
         return True
-    if os.path.isdir('/root/reference/tvdcn/csrc'):
-        build_ref.build('/root/reference')
+    if build_ref.reference_present():
+        build_ref.build()
         return build_ref.load()
     return False
 
@@ -233,6 +233,17 @@ def time_reference(cfg: Config, sample_batch: int, steps: int, warmup: int, seed
     return sample_batch / dt, dt
 
 
+def reference_sample_size(cfg: Config, wanted: float) -> int:
+    """Images per timed pass of the reference: the reference works through the batch in blocks of
+    n_parallel_imgs = the largest divisor of the batch that is <= 32 (32 at the configurations' full sizes), so
+    the sample is a multiple of 32 wherever the configuration has that many images -- its blocking, column
+    buffer and GEMM shapes are then the ones of the full workload."""
+    nb = int(max(1, min(cfg.batch, wanted)))
+    if cfg.batch >= 32:
+        nb = max(32, nb // 32 * 32)
+    return nb
+
+
 def cpu_baseline(cfg: Config, seed: int, budget_s: float = 15.0):
     """Bounded sample of the workload on the host cores: about `budget_s` seconds of CPU work."""
     if not load_reference():
@@ -240,7 +251,7 @@ def cpu_baseline(cfg: Config, seed: int, budget_s: float = 15.0):
     probe = min(2, cfg.batch)
     ips, dt = time_reference(cfg, probe, 1, 1, seed)
     per_image = dt / probe
-    nb = int(max(probe, min(cfg.batch, budget_s / 2 / max(per_image, 1e-9))))
+    nb = reference_sample_size(cfg, budget_s / 2 / max(per_image, 1e-9))
     ips, dt = time_reference(cfg, nb, 2, 0, seed)
     return {'value': ips, 'unit': 'images/s', 'cores': os.cpu_count(), 'kind': 'reference',
             'sample': f'{nb} of {cfg.batch} images of the same workload, fp32, 2 timed fwd+bwd passes, '
@@ -273,7 +284,7 @@ def run_reference_arm(args, cfg):
     probe = min(2, cfg.batch)
     _, dt = time_reference(cfg, probe, 1, 1, seed)
     total = max(args.steps + args.warmup, 1)
-    nb = int(max(1, min(cfg.batch, 120.0 / total / max(dt / probe, 1e-9))))
+    nb = reference_sample_size(cfg, 120.0 / total / max(dt / probe, 1e-9))
     ips, dt = time_reference(cfg, nb, args.steps, args.warmup, seed)
     flops = 3 * cfg.flops_per_pass(nb)
     line = {

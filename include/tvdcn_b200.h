@@ -205,6 +205,17 @@ const char *tvdcn_b200_last_error(void);
  * device, returns the word (0 = no kernel reported a problem, -1 = the query itself failed) and clears it. */
 int tvdcn_b200_device_status(void);
 
+/* Device address of that status word on the current device (NULL if it cannot be found).  A caller that must not
+ * synchronise can copy the word to pinned host memory behind its own work (cudaMemcpyAsync on its stream) and look
+ * at the copy later; the PyTorch front end does that after every operator call and raises at the next one. */
+const int *tvdcn_b200_device_status_address(void);
+
+/* Self test of the bounded waits: launches, on `cuda_stream`, one small kernel that waits (at most `max_polls`
+ * polls of about 20 microseconds, 1 <= max_polls <= 4096) on a barrier nothing ever arrives on, gives up and
+ * records code 900 in the status word -- the path a real kernel takes when a wait runs out.  No counterpart in
+ * the reference, whose kernels never wait. */
+int tvdcn_b200_selftest_bounded_wait(int max_polls, void *cuda_stream);
+
 /* Number of kernels this library has launched in this process so far (monotonic). */
 uint64_t tvdcn_b200_launch_count(void);
 

@@ -52,6 +52,18 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT_DIR = HERE / "_ref"
+
+
+def reference_dir() -> Path:
+    """Where the reference checkout (the tvdcn project) is looked for: $TVDCN_REFERENCE_DIR, else a directory
+    `reference` beside this repository."""
+    env = os.environ.get("TVDCN_REFERENCE_DIR")
+    return Path(env) if env else Path(__file__).resolve().parent.parent.parent / "reference"
+
+
+def reference_present() -> bool:
+    return (reference_dir() / "tvdcn" / "csrc").is_dir()
+
 LIB_NAME = "libtvdcn_ref.so"
 CUDA_LIB_NAME = "libtvdcn_ref_cuda.so"
 
@@ -74,9 +86,9 @@ def _compile_one(src: Path, obj: Path, flags: list[str]) -> None:
         raise RuntimeError(f"compiling {src} failed:\n{res.stderr.decode()[-4000:]}")
 
 
-def build(reference: str | os.PathLike = "/root/reference", jobs: int | None = None,
+def build(reference: str | os.PathLike | None = None, jobs: int | None = None,
           force: bool = False) -> Path:
-    ref = Path(reference)
+    ref = Path(reference) if reference is not None else reference_dir()
     lib = OUT_DIR / LIB_NAME
     srcs = _sources(ref)
     if not srcs or not all(s.exists() for s in srcs):
@@ -113,10 +125,10 @@ def build(reference: str | os.PathLike = "/root/reference", jobs: int | None = N
     return lib
 
 
-def build_cuda(reference: str | os.PathLike = "/root/reference", jobs: int | None = None,
+def build_cuda(reference: str | os.PathLike | None = None, jobs: int | None = None,
                force: bool = False) -> Path:
     """The reference's CUDA kernels and host orchestration -> oracle/_ref/libtvdcn_ref_cuda.so (sm_100)."""
-    ref = Path(reference)
+    ref = Path(reference) if reference is not None else reference_dir()
     lib = OUT_DIR / CUDA_LIB_NAME
     cuda_dir = ref / "tvdcn" / "csrc" / "ops" / "cuda"
     cu = sorted(cuda_dir.glob("*.cu"))
@@ -197,7 +209,7 @@ def load() -> bool:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=None, help="reference checkout (default: $TVDCN_REFERENCE_DIR, else ../reference)")
     ap.add_argument("--jobs", type=int, default=None)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--cuda", action="store_true", help="also build the reference's CUDA backend")

@@ -12,6 +12,7 @@
 #include "../../include/tvdcn_b200.h"
 #include "kernels.h"
 #include "plan.h"
+#include "sm100_ptx.cuh"
 
 namespace tvdcn_b200 {
 
@@ -243,6 +244,20 @@ static cudaError_t run_sample_wgrad_tc(const tvdcn_problem *p, const GeoHost &g,
     }
     return launch_sample_wgrad_tc(g, mode, d_hi, d_lo, ws + pl.img_cl, (const float *)offset, (const float *)mask,
                                   (float *)gw_acc, status, stream);
+}
+
+// Waits on a barrier that nothing arrives on, with a small poll limit, and reports the time-out the way the
+// tensor-core kernels do.
+__global__ void bounded_wait_selftest_kernel(int *status, uint32_t max_polls) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1);
+        ptx::fence_mbar_init();
+    }
+    __syncthreads();
+    bool done = false;
+    for (uint32_t i = 0; i < max_polls && !done; ++i) done = ptx::mbar_try_wait(&bar, 0);
+    if (!done && threadIdx.x == 0) atomicExch(status, 900);
 }
 
 }  // namespace tvdcn_b200
@@ -535,6 +550,16 @@ int tvdcn_b200_mask_softmax_backward(int32_t dtype, int64_t batch, int64_t mask_
     return TVDCN_OK;
 }
 
+int tvdcn_b200_selftest_bounded_wait(int max_polls, void *cuda_stream) {
+    if (max_polls < 1 || max_polls > 4096) return fail(TVDCN_ERR_INVALID, "max_polls must be in [1, 4096]");
+    int *status = device_status_word();
+    if (status == nullptr) return fail(TVDCN_ERR_CUDA, "status word not found");
+    count_launch();
+    bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)cuda_stream>>>(status, (uint32_t)max_polls);
+    CUDA_TRY(cudaGetLastError());
+    return TVDCN_OK;
+}
+
 int tvdcn_b200_cuda_version(void) { return CUDART_VERSION; }
 
 const char *tvdcn_b200_cuda_arch_flags(void) { return "sm_100a"; }
@@ -584,6 +609,8 @@ int tvdcn_b200_device_status(void) {
     if (value != 0) cudaMemset(word, 0, sizeof(int));
     return value;
 }
+
+const int *tvdcn_b200_device_status_address(void) { return device_status_word(); }
 
 uint64_t tvdcn_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

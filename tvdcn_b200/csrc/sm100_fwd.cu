@@ -4,7 +4,7 @@
 //
 // It is an implicit GEMM  D[128 positions x BN dense channels] += A[128 x 64] * B[BN x 64]^T  over K chunks
 // of 64 channels of one kernel tap.  The A tile (the im2col columns of the reference,
-// tvdcn/csrc/ops/cuda/deform_conv2d_common_kernels.cu:138-192) is never written to global memory: eight
+// tvdcn/csrc/ops/cuda/deform_conv2d_common_kernels.cu:138-192) is never written to global memory: sixteen
 // producer warps sample a channels-last copy of the image straight into the 128-byte-swizzled shared
 // memory layout the tensor core reads.  The B tile (weights packed per tap) arrives by TMA.  One thread
 // issues tcgen05.mma with the accumulator in tensor memory; the producer warps then read it back
@@ -36,8 +36,6 @@ struct FwdParams {
     int stages;
     int chunks_per_tap;     // csg / 64
     int prefetch;           // planners also issue L1 prefetches of the corner rows
-    long long *prof;        // optional cycle counters of CTA 0 (tuning aid), else null
-    long long *trace;       // optional per-chunk event times of the middle CTA [8 events][64 chunks], else null
 };
 
 namespace {
@@ -149,19 +147,12 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
     // same slab of the image, which then stays in L1 for all of them
     auto chunk_tap = [&](int j) { return j % g.K; };
     auto chunk_chan0 = [&](int j) { return grp * g.csg + (j / g.K) * CHUNK_C; };
-    const bool trace_cta = P.trace != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0;
-    auto mark = [&](int ev, int j) {
-        if (trace_cta && j < 64) P.trace[ev * 64 + j] = clock64();
-    };
 
     if (warp < PRODUCER_WARPS) {
         // ------------------------------------------------------------------ producers
         const int t = threadIdx.x;
         // position this thread stores in the epilogue (TMEM lane of its warp)
         const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + (warp & 3) * 32 + lane);
-        const bool prof_on = P.prof != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0 && t == 0;
-        long long t_wait = 0, t_prod = 0, t_sig = 0, t_plan = 0, t0 = 0, t_begin = 0;
-        if (prof_on) t_begin = clock64();
         bool ok = true;
         // Two groups of producer warps take alternate chunks, so that one group's loads are in flight while the
         // other blends and stores: the load/store pipe stays busy instead of idling between phases.
@@ -170,39 +161,26 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
         for (int j = pgroup; j < n_chunks; j += PGROUPS) {
             const int s = j % S, r = j / S;
             const int pbuf = j % PLAN_BUFS;
-            if (prof_on) t0 = clock64();
-            if (tg == 0) mark(6, j);
             if (ok && !ptx::mbar_wait(&plan_full[pbuf], (uint32_t)((j / PLAN_BUFS) & 1))) {
                 atomicExch(P.status, 105);
                 ok = false;
             }
-            if (prof_on) { const long long t1 = clock64(); t_plan += t1 - t0; t0 = t1; }
             if (ok && !ptx::mbar_wait(&empty[s], (uint32_t)((r & 1) ^ 1))) {
                 atomicExch(P.status, 101);
                 ok = false;
             }
             ok = __all_sync(0xffffffffu, ok);  // keep the warp converged for the __syncwarp below
-            if (prof_on) { const long long t1 = clock64(); t_wait += t1 - t0; t0 = t1; }
             if (!ok) break;
-            if (tg == 0) mark(1, j);
             uint8_t *a_hi = sA + (size_t)s * a_stage_bytes;
             const uint32_t c16 = (uint32_t)chunk_chan0(j) * ESZ / 16u;
             produce_tiles<NC, MODE, GROUP_THREADS, 2>(a_hi, a_hi + A_TILE_BYTES, 0u, TILE_POS, TILE_POS, img16, &c16,
                                                    plan + pbuf * TILE_POS * NC, tg);
-            if (prof_on) { const long long t1 = clock64(); t_prod += t1 - t0; t0 = t1; }
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
                 ptx::mbar_arrive(&full_a[s]);
                 ptx::mbar_arrive(&plan_empty[pbuf]);
             }
-            if (tg == 0) mark(2, j);
-            if (prof_on) { const long long t1 = clock64(); t_sig += t1 - t0; t0 = t1; }
-        }
-        if (prof_on) {
-            P.prof[0] = t_wait; P.prof[1] = t_prod; P.prof[2] = t_sig; P.prof[3] = t_plan; P.prof[4] = n_chunks;
-            P.prof[5] = clock64() - t_begin;
-            t0 = clock64();
         }
 
         // ------------------------------------------------------------------ epilogue
@@ -242,45 +220,42 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                 }
             }
         }
-        if (prof_on) P.prof[6] = clock64() - t0;
     } else if (warp == PRODUCER_WARPS) {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
             const uint32_t idesc = ptx::instr_desc_f16(MODE == TC_F16 ? 0 : 1, TILE_POS, BN, 0, 0);
             bool ok = true;
-            const bool prof_on = P.prof != nullptr && blockIdx.x == gridDim.x / 2 && blockIdx.y == 0;
-            long long m_wa = 0, m_wb = 0, m_t0 = 0;
+            // ring position, phase and accumulator are stepped, and the descriptors of a stage derived from those of
+            // stage 0 by an addition: this single thread must not spend longer on bookkeeping than on issuing MMAs
+            const uint64_t a_desc0 = ptx::smem_desc_sw128(ptx::smem_u32(sA), 16, 1024);
+            const uint64_t b_desc0 = ptx::smem_desc_sw128(ptx::smem_u32(sB), 16, 1024);
+            int s = 0, acc_i = 0;
+            uint32_t phase = 0;
             for (int j = 0; j < n_chunks && ok; ++j) {
-                const int s = j % S, r = j / S;
-                if (prof_on) m_t0 = clock64();
-                const bool got_a = ptx::mbar_wait(&full_a[s], (uint32_t)(r & 1));
-                if (prof_on) { const long long t1 = clock64(); m_wa += t1 - m_t0; m_t0 = t1; }
-                const bool got_b = got_a && ptx::mbar_wait(&full_b[s], (uint32_t)(r & 1));
-                if (prof_on) { const long long t1 = clock64(); m_wb += t1 - m_t0; P.prof[8] = m_wa; P.prof[9] = m_wb; }
+                const bool got_b = ptx::mbar_wait(&full_a[s], phase) && ptx::mbar_wait(&full_b[s], phase);
                 if (!got_b) {
                     atomicExch(P.status, 103);
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after();
-                mark(3, j);
-                const uint32_t a_addr = ptx::smem_u32(sA + (size_t)s * a_stage_bytes);
-                const uint32_t b_addr = ptx::smem_u32(sB + (size_t)s * b_stage_bytes);
+                const uint64_t a_hi = a_desc0 + (uint64_t)((uint32_t)s * (a_stage_bytes >> 4));
+                const uint64_t b_hi = b_desc0 + (uint64_t)((uint32_t)s * (b_stage_bytes >> 4));
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc_i * BN);
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) {
-                    const uint64_t a_hi = ptx::smem_desc_sw128(a_addr + k4 * 32, 16, 1024);
-                    const uint64_t b_hi = ptx::smem_desc_sw128(b_addr + k4 * 32, 16, 1024);
-                    const uint32_t d_tmem = tmem_base + (uint32_t)((j % NACC) * BN);
-                    ptx::mma_f16(d_tmem, a_hi, b_hi, idesc, (j >= NACC || k4 > 0) ? 1u : 0u);
+                    ptx::mma_f16(d_tmem, a_hi + 2 * k4, b_hi + 2 * k4, idesc, (j >= NACC || k4 > 0) ? 1u : 0u);
                     if constexpr (SPLIT) {
-                        const uint64_t a_lo = ptx::smem_desc_sw128(a_addr + A_TILE_BYTES + k4 * 32, 16, 1024);
-                        const uint64_t b_lo = ptx::smem_desc_sw128(b_addr + b_part_bytes + k4 * 32, 16, 1024);
-                        ptx::mma_f16(d_tmem, a_lo, b_hi, idesc, 1u);
-                        ptx::mma_f16(d_tmem, a_hi, b_lo, idesc, 1u);
+                        ptx::mma_f16(d_tmem, a_hi + (A_TILE_BYTES >> 4) + 2 * k4, b_hi + 2 * k4, idesc, 1u);
+                        ptx::mma_f16(d_tmem, a_hi + 2 * k4, b_hi + (b_part_bytes >> 4) + 2 * k4, idesc, 1u);
                     }
                 }
                 ptx::mma_commit(&empty[s]);
-                mark(4, j);
+                if (++s == S) {
+                    s = 0;
+                    phase ^= 1u;
+                }
+                if (++acc_i == NACC) acc_i = 0;
             }
             if (ok) ptx::mma_commit(accum);
         }
@@ -288,26 +263,30 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
     } else if (warp == PRODUCER_WARPS + 1) {
         // ------------------------------------------------------------------ TMA: weight tiles
         if (lane == 0) {
-            int issued = 0;
+            int s = 0, tap = 0, cc = 0, last_s = -1;
+            uint32_t e_phase = 1, last_phase = 0;
             for (int j = 0; j < n_chunks; ++j) {
-                const int s = j % S, r = j / S;
-                if (!ptx::mbar_wait(&empty[s], (uint32_t)((r & 1) ^ 1))) {
+                if (!ptx::mbar_wait(&empty[s], e_phase)) {
                     atomicExch(P.status, 104);
                     break;
                 }
-                const int tap = j % g.K, cc = j / g.K;
                 uint8_t *b_dst = sB + (size_t)s * b_stage_bytes;
                 ptx::mbar_arrive_expect_tx(&full_b[s], b_stage_bytes);
-                mark(5, j);
                 ptx::tma_load_4d(b_dst, &tmap_hi, &full_b[s], cc * CHUNK_C, n0, tap, grp);
                 if (SPLIT) ptx::tma_load_4d(b_dst + b_part_bytes, &tmap_lo, &full_b[s], cc * CHUNK_C, n0, tap, grp);
-                issued = j + 1;
+                last_s = s;
+                last_phase = e_phase ^ 1u;
+                if (++s == S) {
+                    s = 0;
+                    e_phase ^= 1u;
+                }
+                if (++tap == g.K) {   // chunk j -> (tap j % K, channel chunk j / K)
+                    tap = 0;
+                    ++cc;
+                }
             }
             // never leave with a copy still in flight into this CTA's shared memory
-            if (issued > 0) {
-                const int j = issued - 1;
-                ptx::mbar_wait(&full_b[j % S], (uint32_t)((j / S) & 1));
-            }
+            if (last_s >= 0) ptx::mbar_wait(&full_b[last_s], last_phase);
         }
         __syncwarp();
     }
@@ -367,7 +346,6 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                 advance(fetch_c);
             }
             advance(cur_c);
-            if (t == 0) mark(7, j);
             bool ok = ptx::mbar_wait(&plan_empty[pbuf], (uint32_t)(((j / PLAN_BUFS) & 1) ^ 1));
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
@@ -392,7 +370,6 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
             }
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&plan_full[pbuf]);
-            if (t == 0) mark(0, j);
             return true;
         };
         RawCoords<DIM> r0, r1, r2;
@@ -673,24 +650,6 @@ int tuning_int(const char *name, int fallback) {
     return x > 0 ? x : fallback;
 }
 
-// Cycle counters of CTA 0, filled only when TVDCN_B200_PROF is set (tuning aid; printed by the launcher).
-__device__ long long g_fwd_prof[16];
-static long long *fwd_prof_buffer() {
-    if (tuning_int("TVDCN_B200_PROF", 0) == 0) return nullptr;
-    void *addr = nullptr;
-    if (cudaGetSymbolAddress(&addr, g_fwd_prof) != cudaSuccess) return nullptr;
-    return (long long *)addr;
-}
-
-// Per-chunk event times of the middle CTA, filled when TVDCN_B200_PROF is 2 (tuning aid).
-__device__ long long g_fwd_trace[8 * 64];
-static long long *fwd_trace_buffer() {
-    if (tuning_int("TVDCN_B200_PROF", 0) < 2) return nullptr;
-    void *addr = nullptr;
-    if (cudaGetSymbolAddress(&addr, g_fwd_trace) != cudaSuccess) return nullptr;
-    return (long long *)addr;
-}
-
 // ---- launcher -----------------------------------------------------------------------------------------
 size_t fwd_tc_smem_bytes(int dim, int mode, int bn, int stages) {
     const int parts = mode == TC_SPLIT ? 2 : 1;
@@ -704,13 +663,15 @@ static size_t fwd_static_smem(int dim) { return (size_t)FWD_MAX_TAPS * dim * siz
 
 // Picks the dense-channel tile and the pipeline depth; returns false when the shape is not covered.
 bool fwd_tc_config(int dim, int mode, int cdg, int *bn, int *stages) {
-    const int cap = mode == TC_SPLIT ? tuning_int("TVDCN_B200_FWD_BN_SPLIT", 256) : 256;
+    static const int cap_split = tuning_int("TVDCN_B200_FWD_BN_SPLIT", 256);
+    static const int max_stages = tuning_int("TVDCN_B200_FWD_STAGES", 3);
+    const int cap = mode == TC_SPLIT ? cap_split : 256;
     // widest tile of dense channels first (the sampled tile is produced once per CTA, so a wider tile divides the
     // sampling work), then the deepest pipeline that fits
     int n = 0, s = 0;
     for (int cand_n : {256, 128, 64}) {
         if (cand_n > cap || cdg % cand_n != 0) continue;
-        for (int cand = tuning_int("TVDCN_B200_FWD_STAGES", 3); cand >= 2; --cand)
+        for (int cand = max_stages; cand >= 2; --cand)
             if (fwd_tc_smem_bytes(dim, mode, cand_n, cand) + fwd_static_smem(dim) <= 227 * 1024) { s = cand; break; }
         if (s != 0) { n = cand_n; break; }
     }
@@ -731,28 +692,6 @@ cudaError_t launch_fwd_tc_t(const GeoHost &h, const FwdParams<DIM> &P, const CUt
     dim3 grid((unsigned)((BP + TILE_POS - 1) / TILE_POS), (unsigned)(h.groups * ((h.Cd / h.groups) / P.bn)));
     LaunchScope scope("dcn_fwd_tc", stream);
     kern<<<grid, FWD_THREADS, smem, stream>>>(P, hi, lo);
-    if (P.prof != nullptr) {
-        long long h[16];
-        cudaStreamSynchronize(stream);
-        if (cudaMemcpy(h, P.prof, sizeof(h), cudaMemcpyDeviceToHost) == cudaSuccess)
-            fprintf(stderr, "[dcn_fwd_tc prof] chunks %lld: producer wait_plan %lld wait_empty %lld sample %lld signal %lld "
-                            "loop %lld epilogue %lld | mma wait_a %lld wait_b %lld (cycles, middle CTA)\n", h[4], h[3], h[0],
-                    h[1], h[2], h[5], h[6], h[8], h[9]);
-    }
-    if (P.trace != nullptr) {
-        static long long tr[8 * 64];
-        cudaStreamSynchronize(stream);
-        if (cudaMemcpy(tr, P.trace, sizeof(tr), cudaMemcpyDeviceToHost) == cudaSuccess) {
-            const int n = (int)std::min<long long>(40, (long long)h.K * P.chunks_per_tap);
-            const long long t00 = tr[7 * 64];
-            fprintf(stderr, "[dcn_fwd_tc trace] chunk: planner(wait_empty done) | producer(wait_plan start done) | "
-                            "mma(start issued) | tma issued   (cycles since the planner's first wait)\n");
-            for (int j = 0; j < n; ++j)
-                fprintf(stderr, "  %2d: %7lld %7lld | %7lld %7lld %7lld | %7lld %7lld | %7lld\n", j, tr[7 * 64 + j] - t00,
-                        tr[0 * 64 + j] - t00, tr[6 * 64 + j] - t00, tr[1 * 64 + j] - t00, tr[2 * 64 + j] - t00,
-                        tr[3 * 64 + j] - t00, tr[4 * 64 + j] - t00, tr[5 * 64 + j] - t00);
-        }
-    }
     return cudaGetLastError();
 }
 
@@ -786,9 +725,8 @@ cudaError_t launch_sample_gemm_tc(const GeoHost &h, int mode, const void *img_cl
         P.bn = bn;
         P.stages = stages;
         P.chunks_per_tap = csg / CHUNK_C;
-        P.prof = fwd_prof_buffer();
-        P.trace = fwd_trace_buffer();
-        P.prefetch = tuning_int("TVDCN_B200_PREFETCH", 0);
+        static const int prefetch = tuning_int("TVDCN_B200_PREFETCH", 0);
+        P.prefetch = prefetch;
         if (mode == TC_BF16) return launch_fwd_tc_t<DIM, TC_BF16>(h, P, hi, lo, stream);
         if (mode == TC_F16) return launch_fwd_tc_t<DIM, TC_F16>(h, P, hi, lo, stream);
         return launch_fwd_tc_t<DIM, TC_SPLIT>(h, P, hi, lo, stream);

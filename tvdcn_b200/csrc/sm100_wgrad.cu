@@ -200,34 +200,42 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
         if (lane == 0) {
             const uint32_t idesc = ptx::instr_desc_f16(MODE == TC_F16 ? 0 : 1, 128, NS * 64, 0, 1);
             bool ok = true;
+            // ring position and phase are stepped and the stage's descriptors derived from those of stage 0 by an
+            // addition: bookkeeping must stay cheap next to the MMAs this single thread issues
+            const uint64_t a_desc0 = ptx::smem_desc_sw128(ptx::smem_u32(sA), 16, 1024);
+            const uint64_t b_desc0 = ptx::smem_desc_sw128(ptx::smem_u32(sB), WG_B_TILE, 1024);
+            int s = 0;
+            uint32_t phase = 0;
             for (int i = 0; i < n_stages && ok; ++i) {
-                const int s = i % S, r = i / S;
-                if (!ptx::mbar_wait(&full_s[s], (uint32_t)(r & 1)) || !ptx::mbar_wait(&full_d[s], (uint32_t)(r & 1))) {
+                if (!ptx::mbar_wait(&full_s[s], phase) || !ptx::mbar_wait(&full_d[s], phase)) {
                     atomicExch(P.status, 203);
                     ok = false;
                     break;
                 }
                 ptx::tc_fence_after();
-                const uint32_t a_addr = ptx::smem_u32(sA + (size_t)s * a_stage_bytes);
-                const uint32_t b_addr = ptx::smem_u32(sB + (size_t)s * b_stage_bytes);
+                const uint64_t a_st = a_desc0 + (uint64_t)((uint32_t)s * (a_stage_bytes >> 4));
+                const uint64_t b_hi0 = b_desc0 + (uint64_t)((uint32_t)s * (b_stage_bytes >> 4));
                 for (int m = 0; m < MT; ++m) {
                     const uint32_t d_tmem = tmem_base + (uint32_t)(m * NS * 64);
-                    const uint32_t am = a_addr + (uint32_t)(m * PARTS * WG_A_TILE);
+                    const uint64_t am = a_st + (uint64_t)((uint32_t)(m * PARTS) * (WG_A_TILE >> 4));
 #pragma unroll
                     for (int k4 = 0; k4 < 4; ++k4) {
-                        // A: K-major rows of 64 positions; B: MN-major, 16 positions = 16 rows of 128 bytes
-                        const uint64_t a_hi = ptx::smem_desc_sw128(am + k4 * 32, 16, 1024);
-                        const uint64_t b_hi = ptx::smem_desc_sw128(b_addr + k4 * 2048, WG_B_TILE, 1024);
+                        // A: K-major rows of 64 positions (32 bytes per K step); B: MN-major, 16 positions = 16 rows
+                        // of 128 bytes (2048 bytes per K step)
+                        const uint64_t a_hi = am + 2 * k4;
+                        const uint64_t b_hi = b_hi0 + 128 * k4;
                         ptx::mma_f16(d_tmem, a_hi, b_hi, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
                         if constexpr (SPLIT) {
-                            const uint64_t a_lo = ptx::smem_desc_sw128(am + WG_A_TILE + k4 * 32, 16, 1024);
-                            const uint64_t b_lo = ptx::smem_desc_sw128(b_addr + b_part_bytes + k4 * 2048, WG_B_TILE, 1024);
-                            ptx::mma_f16(d_tmem, a_lo, b_hi, idesc, 1u);
-                            ptx::mma_f16(d_tmem, a_hi, b_lo, idesc, 1u);
+                            ptx::mma_f16(d_tmem, a_hi + (WG_A_TILE >> 4), b_hi, idesc, 1u);
+                            ptx::mma_f16(d_tmem, a_hi, b_hi + (b_part_bytes >> 4), idesc, 1u);
                         }
                     }
                 }
                 ptx::mma_commit(&empty[s]);
+                if (++s == S) {
+                    s = 0;
+                    phase ^= 1u;
+                }
             }
             if (ok && n_stages > 0) ptx::mma_commit(accum);
         }
@@ -360,7 +368,8 @@ bool wgrad_tc_config(int dim, int mode, int cdg, int P, int *n_sub, int *m_tiles
     int ns = mode == TC_SPLIT ? 2 : 4;
     if (dim == 3 && mode != TC_SPLIT) ns = 4;
     int s = 0;
-    for (int cand = tuning_int("TVDCN_B200_WG_STAGES", 2); cand >= 2; --cand)
+    static const int max_stages = tuning_int("TVDCN_B200_WG_STAGES", 2);
+    for (int cand = max_stages; cand >= 2; --cand)
         if (wgrad_smem_bytes(dim, mode, ns, mt, cand) <= 227 * 1024) { s = cand; break; }
     if (s == 0) return false;
     *n_sub = ns;

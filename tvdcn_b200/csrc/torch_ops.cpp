@@ -23,7 +23,10 @@
 #include <torch/autograd.h>
 #include <torch/library.h>
 
+#include <cuda_runtime.h>
+
 #include <array>
+#include <cstdlib>
 #include <string>
 #include <vector>
 
@@ -242,6 +245,63 @@ Call prepare(const Tensor &input, const Tensor &weight, const OptTensor &offset,
     return c;
 }
 
+// ---- status of the bounded waits, without a synchronisation per call --------------------------------------
+// The tensor-core kernels give up on a barrier wait that runs out and leave a code in a per-device word; their
+// outputs are then incomplete.  After every operator call the word is copied, behind the call's kernels on the same
+// stream, into one pinned host integer per device; the next operator call on that device looks at the copy first
+// and raises.  With TVDCN_B200_CHECK_STATUS=1 every call synchronises and raises itself.
+struct StatusWatch {
+    int *pinned = nullptr;
+    bool tried = false;
+};
+StatusWatch &status_watch(int device) {
+    static StatusWatch per_device[64];
+    StatusWatch &w = per_device[device & 63];
+    if (!w.tried) {
+        w.tried = true;
+        if (cudaHostAlloc(reinterpret_cast<void **>(&w.pinned), sizeof(int), cudaHostAllocDefault) == cudaSuccess)
+            *w.pinned = 0;
+        else
+            w.pinned = nullptr;
+    }
+    return w;
+}
+bool check_every_call() {
+    static const bool on = [] {
+        const char *v = getenv("TVDCN_B200_CHECK_STATUS");
+        return v != nullptr && v[0] == '1';
+    }();
+    return on;
+}
+[[noreturn]] void raise_status(int code) {
+    TORCH_CHECK(false, "tvdcn: a tensor-core kernel of an earlier call gave up on a bounded wait (code ", code,
+                "); the tensors that call returned are incomplete");
+    abort();
+}
+// before an operator's own work
+void check_earlier_calls(int device) {
+    StatusWatch &w = status_watch(device);
+    if (w.pinned == nullptr) return;
+    const int seen = *reinterpret_cast<volatile int *>(w.pinned);
+    if (seen != 0) {
+        *w.pinned = 0;
+        (void)tvdcn_b200_device_status();   // synchronises and clears the device word
+        raise_status(seen);
+    }
+}
+// after an operator's kernels have been enqueued on `stream`
+void watch_this_call(int device, cudaStream_t stream) {
+    if (check_every_call()) {
+        const int code = tvdcn_b200_device_status();
+        if (code != 0) raise_status(code);
+        return;
+    }
+    StatusWatch &w = status_watch(device);
+    const int *word = tvdcn_b200_device_status_address();
+    if (w.pinned != nullptr && word != nullptr)
+        (void)cudaMemcpyAsync(w.pinned, word, sizeof(int), cudaMemcpyDeviceToHost, stream);
+}
+
 Tensor make_workspace(size_t bytes, const Tensor &like) {
     return at::empty({(int64_t)bytes}, like.options().dtype(at::kByte));
 }
@@ -253,6 +313,7 @@ Tensor forward_cuda_impl(const Tensor &input, const Tensor &weight, const OptTen
                          const OptTensor &bias, at::IntArrayRef stride, at::IntArrayRef padding,
                          at::IntArrayRef output_padding, at::IntArrayRef dilation, int64_t groups) {
     c10::cuda::CUDAGuard guard(input.device());
+    check_earlier_calls(input.device().index());
     Call c = prepare<D, TR>(input, weight, offset, mask, bias, stride, padding, output_padding, dilation, groups);
     std::vector<int64_t> shape{c.prob.batch, c.prob.out_channels};
     for (int a = 0; a < D; ++a) shape.push_back(c.prob.out_size[a]);
@@ -264,6 +325,7 @@ Tensor forward_cuda_impl(const Tensor &input, const Tensor &weight, const OptTen
                                                   ptr(c.bias), out.data_ptr(), wsb ? ws.data_ptr() : nullptr, wsb,
                                                   stream.stream());
     TORCH_CHECK(rc == TVDCN_OK, op_name<D, TR>(), ": ", tvdcn_b200_last_error());
+    watch_this_call(input.device().index(), stream.stream());
     if (c.unbatched) out = out.squeeze(0);
     return out;
 }
@@ -274,6 +336,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> backward_cuda_impl(
     const OptTensor &bias, at::IntArrayRef stride, at::IntArrayRef padding, at::IntArrayRef output_padding,
     at::IntArrayRef dilation, int64_t groups) {
     c10::cuda::CUDAGuard guard(input.device());
+    check_earlier_calls(input.device().index());
     Call c = prepare<D, TR>(input, weight, offset, mask, bias, stride, padding, output_padding, dilation, groups);
     Tensor g = grad.contiguous();
     if (c.unbatched) g = g.unsqueeze(0);
@@ -298,6 +361,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> backward_cuda_impl(
         g_mask.defined() ? g_mask.data_ptr() : nullptr, g_bias.defined() ? g_bias.data_ptr() : nullptr,
         wsb ? ws.data_ptr() : nullptr, wsb, stream.stream());
     TORCH_CHECK(rc == TVDCN_OK, "_", op_name<D, TR>(), "_backward: ", tvdcn_b200_last_error());
+    watch_this_call(input.device().index(), stream.stream());
     if (c.unbatched) {
         g_input = g_input.squeeze(0);
         if (g_offset.defined()) g_offset = g_offset.squeeze(0);
