@@ -7,8 +7,16 @@ One "step" is one forward + backward pass of the configured operator over one ba
 tensors (for config 2 the mask is produced by mask_softmax2d inside the step, forward and backward).
 Rank 0 prints ONE JSON line.  Keys beyond the usual ones:
 
-  value        images/s with every input already resident in HBM, all ranks together (weak scaling: each
-               rank owns a full per-GPU batch; the only exchange is the all-reduce of [grad_weight|grad_bias])
+  value        images/s with every input already resident in HBM, all ranks together.  --gpus N shards the
+               configuration's batch over the ranks (strong scaling, config 2: 128 / 64 / 32 / 16 images per
+               rank); the only exchange is the all-reduce of [grad_weight|grad_bias].  "weak" carries the figure
+               with the configuration's whole batch on every GPU.
+  modes        the configuration's other data mode (bf16 input / weight for configurations 2 and 5), measured in
+               the same process after the headline mode: value, kernels, roofline, e2e, clocks
+  operator_step_ms  the same device-resident step through the public PyTorch operators (fresh outputs and
+               workspace per call), beside the C-ABI step that `value` times
+  grad_check   N > 1: the all-reduced gradient against the sum of the ranks' buckets and against one GPU computing
+               the whole batch (outside the timed regions)
   e2e          the same metric through the public operators (tvdcn_b200.ops.*, autograd) with HOST buffers:
                pinned host -> device copies of every step's inputs and device -> host copies of its results
                are inside the timed region, on copy streams beside the compute stream (prefetching loader)
@@ -290,7 +298,7 @@ def run_reference_arm(args, cfg):
     line = {
         'impl': 'reference', 'metric': METRIC, 'value': ips, 'unit': 'images/s', 'n_gpus': args.gpus,
         'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': dt * 1e3, 'higher_is_better': True,
-        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic (seeded, CPU generator)',
+        'scaling': args.scaling, 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic (seeded, CPU generator)',
         'config': {'workload': cfg.name, 'sample_images_per_step': nb},
         'effective_tflops': flops / dt / 1e12,
         'cpu_baseline': {'value': ips, 'unit': 'images/s', 'cores': os.cpu_count(), 'kind': 'reference',
@@ -500,6 +508,35 @@ class HostStep:
                 cur.wait_event(ev)
 
 
+class OperatorStep:
+    """The device-resident step through the public operators (torch.ops.tvdcn.* via tvdcn_b200.ops, autograd):
+    every call allocates its outputs and workspace and stages its own inputs, unlike the C-ABI step of `value`."""
+
+    def __init__(self, cfg: Config, ts, mode: str, device):
+        import tvdcn_b200
+        self.ops, self.cfg = tvdcn_b200.ops, cfg
+        dt = torch.bfloat16 if mode == 'bf16' else torch.float32
+        self.x = ts['x'].to(device, dt).requires_grad_(True)
+        self.w = ts['w'].to(device, dt).requires_grad_(True)
+        self.go = ts['go'].to(device, dt)
+        self.off = ts['off'].to(device).requires_grad_(True)
+        self.m = ts['m'].to(device).requires_grad_(True)
+        self.bias = ts['bias'].to(device).requires_grad_(True)
+
+    def __call__(self):
+        cfg, ops = self.cfg, self.ops
+        for t in (self.x, self.w, self.off, self.m, self.bias):
+            t.grad = None
+        mask = getattr(ops, f'mask_softmax{cfg.dim}d')(self.m, cfg.kernel) if cfg.softmax_mask else self.m
+        if cfg.transposed:
+            out = getattr(ops, f'deform_conv_transpose{cfg.dim}d')(self.x, self.w, self.off, mask, self.bias,
+                                                                   cfg.stride, cfg.padding, 0, cfg.dilation, cfg.groups)
+        else:
+            out = getattr(ops, f'deform_conv{cfg.dim}d')(self.x, self.w, self.off, mask, self.bias, cfg.stride,
+                                                         cfg.padding, cfg.dilation, cfg.groups)
+        out.backward(self.go)
+
+
 def timed(fn, steps, warmup, barrier):
     for _ in range(warmup):
         fn()
@@ -538,57 +575,37 @@ def emit(line: str):
         os.write(_RESULT_FD, (line + '\n').encode())
 
 
-def main():
-    claim_stdout()
-    ap = argparse.ArgumentParser()
-    ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=50)
-    ap.add_argument('--warmup', type=int, default=5)
-    ap.add_argument('--config', type=int, default=2, choices=sorted(CONFIGS))
-    ap.add_argument('--mode', default='fp32', choices=['fp32', 'bf16'])
-    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--batch', type=int, default=0, help='per-GPU batch (default: the configuration\'s)')
-    ap.add_argument('--no-cpu-baseline', action='store_true')
-    ap.add_argument('--no-e2e', action='store_true')
-    ap.add_argument('--no-ref-cuda', action='store_true',
-                    help="skip timing the reference's own CUDA backend (oracle/_ref/libtvdcn_ref_cuda.so, fp32) on "
-                         'this GPU, reported as "reference_cuda" (1 GPU only)')
-    args = ap.parse_args()
-    cfg = CONFIGS[args.config]
-    if args.warmup < 3 and args.impl == 'ours':
-        args.warmup = 3
+def dominant_roofline(cfg: Config, kernels: dict, batch: int, config_index: int, mode: str, pk: dict):
+    """Roofline entry of the kernel with the largest share of the step."""
+    gemm_like = {'sample_gemm', 'gemm_scatter', 'sample_wgrad', 'dcn_fwd_tc', 'dcn_wgrad_tc', 'dcn_dgrad_tc'}
+    if not kernels:
+        return None
+    dom = max(kernels, key=lambda k: kernels[k]['ms_per_step'])
+    ms = kernels[dom]['ms_per_launch']
+    if cfg.bound == 'tensor' and dom in gemm_like:
+        ach = cfg.flops_per_pass(batch) / (ms / 1e3) / 1e12
+        # a kernel of about a millisecond timed by events between other kernels: the burst figure is the denominator
+        peak = pk['tflops_burst']
+        return {'kernel': dom, 'bound': 'tensor', 'achieved': ach, 'peak': peak, 'unit': 'TFLOP/s',
+                'frac': ach / peak, 'frac_of_sustained': ach / pk['tflops_sustained'],
+                'traffic': known_traffic(dom, config_index, mode),
+                'peak_source': pk['source'] + ' bf16 dense, burst (of measured)',
+                'note': 'algorithmic FLOPs of one GEMM pass (2*Cout*Cin/g*taps*N*P) / CUDA-event time'}
+    # share of the step's algorithmic bytes: a GEMM-shaped kernel touches about a third of them
+    share = cfg.algorithmic_bytes(batch) / 3 if dom in gemm_like else cfg.algorithmic_bytes(batch)
+    ach = share / (ms / 1e3) / 1e9
+    return {'kernel': dom, 'bound': 'hbm', 'achieved': ach, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
+            'frac': ach / pk['hbm_gbs'], 'traffic': known_traffic(dom, config_index, mode),
+            'peak_source': pk['source'] + ' copy bandwidth (of measured)'}
 
-    if args.impl == 'reference':
-        run_reference_arm(args, cfg)
-        return
 
+def measure_mode(cfg: Config, config_index: int, mode: str, ts, batch: int, device, bucket, world: int, barrier,
+                 args, L, local: int, want_e2e: bool):
+    """One data mode of the step on this rank's batch shard: device-resident throughput, per-kernel times, the
+    roofline of the dominant kernel, the end-to-end figure and the clocks seen during the timed region."""
     import torch.distributed as dist
-    from tvdcn_b200 import cabi
-    from tvdcn_b200.data_parallel import GradBucket
-
-    world = int(os.environ.get('WORLD_SIZE', '1'))
-    rank = int(os.environ.get('RANK', '0'))
-    local = int(os.environ.get('LOCAL_RANK', '0'))
-    assert torch.cuda.is_available(), 'bench.py needs a CUDA device; there is no CPU fallback'
-    torch.cuda.set_device(local)
-    device = torch.device('cuda', local)
-    if world > 1:
-        dist.init_process_group('nccl', device_id=device)
-    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
-
-    batch = args.batch or cfg.batch
-    seed = 1000 + args.config + 7919 * rank
-    ts = make_inputs(cfg, batch, seed, pin=not args.no_e2e)
-    wshape = ts['w'].shape
-    bucket = GradBucket(wshape, cfg.cout, dtype=torch.float32, device=device)
-    L = cabi.lib()
-    L.tvdcn_b200_timing_enable.argtypes = [ctypes.c_int]
-    L.tvdcn_b200_timing_report.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
-    L.tvdcn_b200_timing_report.restype = ctypes.c_size_t
-
-    step = DeviceStep(cfg, ts, args.mode, device, bucket)
+    step = DeviceStep(cfg, ts, mode, device, bucket)
     with ClockSampler(local) as clocks:
-        launches0 = L.tvdcn_b200_launch_count()
         for _ in range(args.warmup):
             step()
         launches1 = L.tvdcn_b200_launch_count()
@@ -598,7 +615,8 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     secs = t.item()
-    value = batch * world * args.steps / secs
+    global_batch = batch_total(batch, device, world)
+    value = global_batch * args.steps / secs
 
     # per-kernel durations for the roofline: same step, kernels bracketed by CUDA events
     L.tvdcn_b200_timing_enable(1)
@@ -615,38 +633,173 @@ def main():
         kernels[name] = {'launches_per_step': int(n) / ksteps, 'ms_per_launch': float(ms) / int(n),
                          'ms_per_step': float(ms) / ksteps}
     pk = peaks()
-    gemm_like = {'sample_gemm', 'gemm_scatter', 'sample_wgrad', 'dcn_fwd_tc', 'dcn_wgrad_tc', 'dcn_dgrad_tc'}
-    dom = max(kernels, key=lambda k: kernels[k]['ms_per_step']) if kernels else None
-    roofline = None
-    if dom is not None:
-        ms = kernels[dom]['ms_per_launch']
-        if cfg.bound == 'tensor' and dom in gemm_like:
-            passes = 2 if (cfg.transposed and dom == 'gemm_scatter') else 1
-            ach = cfg.flops_per_pass(batch) / (ms / 1e3) / 1e12
-            peak = pk['tflops_sustained']
-            roofline = {'kernel': dom, 'bound': 'tensor', 'achieved': ach, 'peak': peak, 'unit': 'TFLOP/s',
-                        'frac': ach / peak, 'traffic': known_traffic(dom, args.config, args.mode),
-                        'peak_source': pk['source'] + ' bf16 dense, sustained',
-                        'note': 'algorithmic FLOPs of one GEMM pass (2*Cout*Cin/g*taps*N*P) / CUDA-event time'}
-        else:
-            # share of the step's algorithmic bytes: a GEMM-shaped kernel touches about a third of them
-            share = cfg.algorithmic_bytes(batch) / 3 if dom in gemm_like else cfg.algorithmic_bytes(batch)
-            ach = share / (ms / 1e3) / 1e9
-            roofline = {'kernel': dom, 'bound': 'hbm', 'achieved': ach, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
-                        'frac': ach / pk['hbm_gbs'], 'traffic': known_traffic(dom, args.config, args.mode),
-                        'peak_source': pk['source'] + ' copy bandwidth'}
+    roofline = dominant_roofline(cfg, kernels, batch, config_index, mode, pk)
 
-    # end to end through the public operators with host buffers
+    # the same step through the public operators (fresh workspace and outputs per call, no staging reuse), still on
+    # device-resident tensors: what a PyTorch user of the operators sees beside the C-ABI figure above
     e2e = None
-    if not args.no_e2e:
-        host = HostStep(cfg, ts, args.mode, device, bucket)
+    ops_step_ms = None
+    if want_e2e:
+        host = HostStep(cfg, ts, mode, device, bucket)
         esteps = max(3, min(args.steps, 10))
         esecs = timed(host, esteps, 2, barrier)
         t = torch.tensor([esecs], device=device, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e = {'value': batch * world * esteps / t.item(), 'unit': 'images/s', 'h2d_bytes_per_step': host.h2d,
+        e2e = {'value': global_batch * esteps / t.item(), 'unit': 'images/s', 'h2d_bytes_per_step': host.h2d,
                'd2h_bytes_per_step': host.d2h, 'steps': esteps}
+        ops = OperatorStep(cfg, ts, mode, device)
+        ops_step_ms = timed(ops, esteps, 2, barrier) / esteps * 1e3
+    step_s = secs / args.steps
+    flops = 3 * cfg.flops_per_pass(global_batch)
+    nbytes = cfg.algorithmic_bytes(global_batch, 4 if mode == 'fp32' else 2)
+    return {
+        'value': value, 'unit': 'images/s', 'ms_per_step': step_s * 1e3,
+        'dtype': 'f32' if mode == 'fp32' else 'bf16 input/weight, f32 accumulate, f32 offset/mask',
+        'effective_tflops': flops / step_s / 1e12,
+        'tensor_frac_of_peak': flops / step_s / 1e12 / pk['tflops_sustained'] / world,
+        'algorithmic_gbs': nbytes / step_s / 1e9,
+        'hbm_frac_of_peak': nbytes / step_s / 1e9 / pk['hbm_gbs'] / world,
+        'kernels': kernels, 'roofline': roofline, 'e2e': e2e, 'operator_step_ms': ops_step_ms,
+        'gpu_launches': int(launches2 - launches1), 'clocks': clocks.summary(), 'engine_fwd_bwd': step.engine,
+    }, step
+
+
+def batch_total(batch: int, device, world: int) -> int:
+    """Images all ranks process per step (the shards may differ by one image)."""
+    if world == 1:
+        return batch
+    import torch.distributed as dist
+    t = torch.tensor([batch], device=device, dtype=torch.int64)
+    dist.all_reduce(t)
+    return int(t.item())
+
+
+def check_reduced_gradient(cfg: Config, step, ts_global, device, world: int, rank: int):
+    """Outside every timed region: the all-reduced [grad_weight | grad_bias] must equal (a) the sum of the ranks'
+    own buckets and (b), on rank 0, the gradient one GPU computes for the whole global batch.  Returns the two
+    normalised max errors (rank 0), which must be <= 1e-5 for f32 data."""
+    import torch.distributed as dist
+    from tvdcn_b200.data_parallel import GradBucket
+    bucket = step.bucket
+    step()                                   # fills and all-reduces the bucket
+    torch.cuda.synchronize()
+    reduced = bucket.flat.clone()
+    # (a) local buckets: the same step with the exchange switched off
+    saved = bucket.all_reduce_async
+    bucket.all_reduce_async = lambda: None
+    step()
+    torch.cuda.synchronize()
+    bucket.all_reduce_async = saved
+    local = bucket.flat.clone()
+    parts = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(parts, local)
+    total = torch.stack(parts).double().sum(0)
+    denom = total.abs().max().clamp_min(1e-30)
+    err_sum = ((reduced.double() - total).abs().max() / denom).item()
+    err_one = None
+    if rank == 0 and ts_global is not None:
+        solo = GradBucket(ts_global['w'].shape, cfg.cout, dtype=torch.float32, device=device)
+        solo.all_reduce_async = lambda: None     # rank 0 alone: no collective
+        one = DeviceStep(cfg, ts_global, 'fp32', device, solo)
+        one()
+        torch.cuda.synchronize()
+        err_one = ((reduced.double() - solo.flat.double()).abs().max() / denom).item()
+        del one, solo
+    return {'vs_sum_of_rank_buckets': err_sum, 'vs_one_gpu_whole_batch': err_one, 'tolerance': 1e-5}
+
+
+def main():
+    claim_stdout()
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=50)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--config', type=int, default=2, choices=sorted(CONFIGS))
+    ap.add_argument('--mode', default='fp32', choices=['fp32', 'bf16'],
+                    help='data mode of the headline figures; the other mode of configurations 2 and 5 is measured in '
+                         'the same run and reported under "modes"')
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--scaling', default='strong', choices=['strong', 'weak'],
+                    help='strong (default): the configuration\'s batch is sharded over the GPUs; weak: every GPU '
+                         'gets the configuration\'s whole batch')
+    ap.add_argument('--batch', type=int, default=0, help='global batch (default: the configuration\'s)')
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--no-other-mode', action='store_true', help='measure only --mode')
+    ap.add_argument('--no-ref-cuda', action='store_true',
+                    help="skip timing the reference's own CUDA backend (oracle/_ref/libtvdcn_ref_cuda.so, fp32) on "
+                         'this GPU, reported as "reference_cuda" (1 GPU only)')
+    args = ap.parse_args()
+    cfg = CONFIGS[args.config]
+    if args.warmup < 3 and args.impl == 'ours':
+        args.warmup = 3
+
+    if args.impl == 'reference':
+        run_reference_arm(args, cfg)
+        return
+
+    import torch.distributed as dist
+    from tvdcn_b200 import cabi
+    from tvdcn_b200.data_parallel import GradBucket, shard_bounds
+
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    rank = int(os.environ.get('RANK', '0'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    assert torch.cuda.is_available(), 'bench.py needs a CUDA device; there is no CPU fallback'
+    torch.cuda.set_device(local)
+    device = torch.device('cuda', local)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+
+    # Strong scaling: every rank generates the same global batch (CPU generator, seed 1000 + config) and keeps its
+    # contiguous slice; weights and bias are replicas.  Weak scaling: every rank has a whole batch of its own.
+    global_batch = args.batch or cfg.batch
+    pin = not args.no_e2e
+    ts_global = None
+    if args.scaling == 'strong':
+        ts_global = make_inputs(cfg, global_batch, 1000 + args.config)
+        b0, b1 = shard_bounds(global_batch, rank, world)
+        ts = {k: (v if k in ('w', 'bias') else v[b0:b1].contiguous()) for k, v in ts_global.items()}
+        if pin:
+            ts = {k: v.pin_memory() for k, v in ts.items()}
+        batch = b1 - b0
+        if world == 1 or rank != 0:
+            ts_global = None
+    else:
+        batch = global_batch
+        ts = make_inputs(cfg, batch, 1000 + args.config + 7919 * rank, pin=pin)
+    assert batch > 0, 'more GPUs than images'
+    bucket = GradBucket(ts['w'].shape, cfg.cout, dtype=torch.float32, device=device)
+    L = cabi.lib()
+    L.tvdcn_b200_timing_enable.argtypes = [ctypes.c_int]
+    L.tvdcn_b200_timing_report.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+    L.tvdcn_b200_timing_report.restype = ctypes.c_size_t
+
+    head, step = measure_mode(cfg, args.config, args.mode, ts, batch, device, bucket, world, barrier, args, L, local,
+                              not args.no_e2e)
+    grad_check = None
+    if world > 1 and args.mode == 'fp32':
+        grad_check = check_reduced_gradient(cfg, step, ts_global, device, world, rank)
+    del step
+    modes = {}
+    other = 'bf16' if args.mode == 'fp32' else 'fp32'
+    if not args.no_other_mode and args.config in (2, 5):
+        modes[other], _ = measure_mode(cfg, args.config, other, ts, batch, device, bucket, world, barrier, args, L,
+                                       local, not args.no_e2e)
+        del _
+    # the other way of scaling, device-resident figure only
+    weak = None
+    if world > 1 and args.scaling == 'strong':
+        tw = make_inputs(cfg, cfg.batch, 1000 + args.config + 7919 * rank)
+        wstep = DeviceStep(cfg, tw, args.mode, device, bucket)
+        wsecs = timed(wstep, args.steps, args.warmup, barrier)
+        t = torch.tensor([wsecs], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        weak = {'value': cfg.batch * world * args.steps / t.item(), 'unit': 'images/s',
+                'ms_per_step': t.item() / args.steps * 1e3, 'per_gpu_batch': cfg.batch}
+        del wstep, tw
 
     base = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -660,25 +813,24 @@ def main():
             ref_cuda = {'unavailable': f'{type(e).__name__}: {e}'[:200]}
 
     if rank == 0:
-        flops = 3 * cfg.flops_per_pass(batch) * world
-        step_s = secs / args.steps
-        nbytes = cfg.algorithmic_bytes(batch, 4) * world
+        total = head['value'] * head['ms_per_step'] / 1e3     # images per step, all ranks
+        nbytes = cfg.algorithmic_bytes(batch, 4)
         line = {
-            'metric': METRIC, 'value': value, 'unit': 'images/s', 'n_gpus': world, 'steps': args.steps,
-            'warmup': args.warmup, 'ms_per_step': step_s * 1e3, 'higher_is_better': True, 'scaling': 'weak',
-            'vs_baseline': None,
-            'dtype': 'f32' if args.mode == 'fp32' else 'bf16 input/weight, f32 accumulate, f32 offset/mask',
+            'metric': METRIC, 'value': head['value'], 'unit': 'images/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': args.warmup, 'ms_per_step': head['ms_per_step'], 'higher_is_better': True,
+            'scaling': args.scaling, 'vs_baseline': None, 'dtype': head['dtype'],
             'data': 'synthetic (seeded, CPU generator)',
             'config': {'workload': cfg.name, 'config_index': args.config, 'per_gpu_batch': batch,
-                       'global_batch': batch * world, 'parallelism': f'dp{world}', 'engine_fwd_bwd': step.engine,
-                       'l2': 'inputs larger than L2 (no flush needed)' if nbytes / world > 126e6 * 2
-                             else 'working set near L2 size; not flushed'},
-            'effective_tflops': flops / step_s / 1e12,
-            'tensor_frac_of_peak': flops / step_s / 1e12 / pk['tflops_sustained'] / world,
-            'algorithmic_gbs': nbytes / step_s / 1e9,
-            'hbm_frac_of_peak': nbytes / step_s / 1e9 / pk['hbm_gbs'] / world,
-            'kernels': kernels, 'roofline': roofline, 'cpu_baseline': base, 'reference_cuda': ref_cuda, 'e2e': e2e,
-            'gpu_launches': int(launches2 - launches1), 'clocks': clocks.summary(),
+                       'global_batch': int(round(total)), 'parallelism': f'dp{world}',
+                       'engine_fwd_bwd': head['engine_fwd_bwd'],
+                       'l2': 'inputs larger than L2 (no flush needed)' if nbytes > 126e6 * 2
+                             else 'working set of one rank near L2 size; not flushed'},
+            'effective_tflops': head['effective_tflops'], 'tensor_frac_of_peak': head['tensor_frac_of_peak'],
+            'algorithmic_gbs': head['algorithmic_gbs'], 'hbm_frac_of_peak': head['hbm_frac_of_peak'],
+            'kernels': head['kernels'], 'roofline': head['roofline'], 'cpu_baseline': base,
+            'reference_cuda': ref_cuda, 'e2e': head['e2e'], 'operator_step_ms': head['operator_step_ms'],
+            'gpu_launches': head['gpu_launches'], 'clocks': head['clocks'],
+            'modes': modes, 'weak': weak, 'grad_check': grad_check,
         }
         emit(json.dumps(line))
     if world > 1:

@@ -7,9 +7,17 @@ Two anchors, both from the reference's CUDA kernels on the same values: its f32 
 run measures this library's own error where the arithmetic is well conditioned; the f32 run is the anchor where
 f32 *coordinates* dominate (at L = 4096 one ulp of a sampling position is 5e-4 px, which moves every result by
 ~1e-4 in both f32 implementations alike) and for grad_offset, which is discontinuous where a sampling position
-crosses an integer (a position that rounds to the other side in f64 flips whole terms).  A tensor passes when
-it is within tolerance of either anchor (grad_offset: of the f32 anchor): 1e-4 normalised max error for f32
-data, 2e-2 for bf16 input / weight.
+crosses an integer (a position that rounds to the other side in f64 flips whole terms).
+
+Rule per tensor (f32 data, tolerance 1e-4, bf16 input / weight 2e-2): the f64 run is the anchor.  The f32 anchor
+is accepted in its place only where the reference disagrees with itself, i.e. where the reference's own f32 run
+is more than 5e-5 away from its f64 run for that tensor -- then f32 arithmetic, not this library, sets the
+error.  Both errors and the reference's own f32-vs-f64 distance are part of every assertion message.
+
+Metric: normalised max error, max|a - ref| / max|ref| per tensor, in f64 (what every tolerance in this suite
+means).  Beside it the element-relative outlier fraction is computed and bounded: the share of elements with
+|a - ref| > 1e-3 |ref| + 1e-5 max|ref| must stay below 1e-4, so that an error confined to small-magnitude
+elements cannot hide behind a large maximum.
 """
 import pytest
 import torch
@@ -43,6 +51,28 @@ def _inputs(case):
     return tuple(None if t is None else t.cuda() for t in ts)
 
 
+def outlier_fraction(a, ref, rtol=1e-3, atol_rel=1e-5):
+    """Share of elements with |a - ref| > rtol |ref| + atol_rel max|ref| (computed on the GPU, in f64)."""
+    a64, r64 = a.double(), ref.double()
+    bound = rtol * r64.abs() + atol_rel * r64.abs().max()
+    return ((a64 - r64).abs() > bound).double().mean().item()
+
+
+def check_against_both_anchors(case, got, ref64, ref32, tol=1e-4):
+    for name, a, r64, r32 in zip(cases.NAMES, got, ref64, ref32):
+        assert a is not None and r64 is not None, name
+        assert torch.isfinite(a).all(), name
+        e64, e32, ref_gap = nerr(a, r64), nerr(a, r32), nerr(r32, r64)
+        anchor, e, r = ('f64', e64, r64)
+        if ref_gap > 5e-5 and e32 < e64:     # the reference's own f32 run is this far from its f64 run
+            anchor, e, r = ('f32', e32, r32)
+        frac = outlier_fraction(a, r)
+        msg = (f'{case.name} {name}: normalised max error vs f64 {e64:.3e}, vs f32 {e32:.3e}; reference f32 vs f64 '
+               f'{ref_gap:.3e}; anchor {anchor}; element-relative outliers {frac:.2e}')
+        assert e <= tol, msg
+        assert frac <= 1e-4, msg
+
+
 @pytest.mark.parametrize('case', FULL, ids=lambda c: c.name)
 def test_full_size_f32(case, reference_cuda):
     x, w, off, mask, bias, go = _inputs(case)
@@ -50,12 +80,29 @@ def test_full_size_f32(case, reference_cuda):
     ref64 = run_reference(case, *(dbl(t) for t in (x, w, off, mask, bias, go)))
     ref32 = run_reference(case, x, w, off, mask, bias, go)
     got = run_cabi(case, x, w, off, mask, bias, go)
-    for name, a, r64, r32 in zip(cases.NAMES, got, ref64, ref32):
-        assert a is not None and r64 is not None, name
-        assert torch.isfinite(a).all(), name
-        e32 = nerr(a, r32)
-        e = e32 if name == 'grad_offset' else min(e32, nerr(a, r64))
-        assert e <= 1e-4, f'{case.name} {name}: normalised max error {e:.3e}'
+    check_against_both_anchors(case, got, ref64, ref32)
+
+
+def test_benchmark_tensors_of_config_2(reference_cuda):
+    """The exact tensors bench.py times at configuration 2 (bench.make_inputs, seed 1002), with the mask produced
+    by this library's tvdcn::mask_softmax2d from the benchmark's logits, as in the benchmark step."""
+    import bench
+    import tvdcn_b200
+    cfg = bench.CONFIGS[2]
+    ts = bench.make_inputs(cfg, cfg.batch, 1002)
+    x, w, off, bias, go = (ts[k].cuda() for k in ('x', 'w', 'off', 'bias', 'go'))
+    logits = ts['m'].cuda()
+    mask = tvdcn_b200.ops.mask_softmax2d(logits, cfg.kernel)
+    ref_mask = torch.softmax(logits.double().view(cfg.batch, cfg.mask_groups, cfg.taps, -1), 2).view_as(logits)
+    assert nerr(mask, ref_mask) <= 1e-6
+    case = FULL[1]
+    assert (case.batch, case.in_channels, case.in_size, case.offset_groups) == (cfg.batch, cfg.cin, cfg.in_size,
+                                                                                cfg.offset_groups)
+    dbl = lambda t: None if t is None else t.double()
+    ref64 = run_reference(case, *(dbl(t) for t in (x, w, off, mask, bias, go)))
+    ref32 = run_reference(case, x, w, off, mask, bias, go)
+    got = run_cabi(case, x, w, off, mask, bias, go)
+    check_against_both_anchors(case, got, ref64, ref32)
 
 
 @pytest.mark.parametrize('case', [FULL[1], FULL[4]], ids=lambda c: c.name)

@@ -1,4 +1,6 @@
-"""The workspace-free forward (tvdcn_b200_deform_conv_forward_static) against the ordinary forward.
+"""The workspace-free forward (tvdcn_b200_deform_conv_forward_static) against the ordinary forward and against
+the CPU oracle (the two forwards share every kernel, so agreement between them alone would not catch a fault
+common to both).
 
 That entry point is for embedders that may not allocate device memory when the operator runs (plugins that
 only receive tensor pointers, arena runtimes that forbid cudaMalloc after start-up): it borrows a fixed
@@ -13,7 +15,7 @@ import pytest
 import torch
 
 import cases
-from cases import Case, make_inputs, nerr
+from cases import Case, make_inputs, nerr, run_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -55,15 +57,20 @@ def _forward_both(case, seed):
                                                        vp(got), stream))
     torch.cuda.synchronize()
     assert L.tvdcn_b200_device_status() == 0
-    return got, ref
+    # the CPU oracle on the same f32 values, in f64
+    dbl = lambda t: None if t is None else t.double().cpu()
+    go = torch.zeros(shape, dtype=torch.float64)
+    oracle = run_oracle(case, dbl(x), dbl(w), dbl(off), dbl(mask), dbl(bias), go)[0]
+    return got, ref, oracle
 
 
 @pytest.mark.parametrize('case', CASES, ids=[c.name for c in CASES])
 def test_static_forward_matches_workspace_forward_twice(case):
     for seed in (71, 72):  # second call reuses the scratch the first one dirtied
-        got, ref = _forward_both(case, seed)
+        got, ref, oracle = _forward_both(case, seed)
         assert torch.isfinite(ref).all()
-        assert nerr(got, ref) <= 1e-4  # the f32 tolerance of the parity tests; in practice the two are equal
+        assert nerr(got, ref) <= 1e-4     # the f32 tolerance of the parity tests; in practice the two are equal
+        assert nerr(got, oracle) <= 1e-4  # and against the oracle, which shares no code with either
 
 
 def test_static_forward_refuses_problems_larger_than_its_scratch():
