@@ -377,6 +377,8 @@ class DeviceStep:
         n = max(self.L.tvdcn_b200_forward_workspace_bytes(pp), self.L.tvdcn_b200_backward_workspace_bytes(pp), 256)
         self.ws = torch.empty(n, dtype=torch.uint8, device=device)
         self.engine = (self.L.tvdcn_b200_engine_name(pp, 0).decode(), self.L.tvdcn_b200_engine_name(pp, 1).decode())
+        self.gw_ready = torch.cuda.Event()
+        self.gw_ready.record()      # creates the underlying cudaEvent_t
 
     def __call__(self):
         cfg, L, cabi = self.cfg, self.L, self.cabi
@@ -390,13 +392,18 @@ class DeviceStep:
                                                          vp(self.mask), st))
         cabi.check(L.tvdcn_b200_deform_conv_forward(pp, vp(self.x), vp(self.w), vp(self.off), vp(self.mask),
                                                     vp(self.bias), vp(self.out), vp(self.ws), self.ws.numel(), st))
-        cabi.check(L.tvdcn_b200_deform_conv_backward(ctypes.byref(self.p_bwd), vp(self.go), vp(self.x), vp(self.w),
-                                                     vp(self.off),
-                                                     vp(self.mask), vp(self.gx), vp(self.gw), vp(self.goff),
-                                                     vp(self.gmask), vp(self.gb), vp(self.ws), self.ws.numel(), st))
+        # the event is recorded when grad_weight / grad_bias are final (on the library's second stream, while the
+        # scatter kernel still runs): the all-reduce starts there, not at the end of the backward pass
+        cabi.check(L.tvdcn_b200_deform_conv_backward_ex(ctypes.byref(self.p_bwd), vp(self.go), vp(self.x),
+                                                        vp(self.w), vp(self.off), vp(self.mask), vp(self.gx),
+                                                        vp(self.gw), vp(self.goff), vp(self.gmask), vp(self.gb),
+                                                        vp(self.ws), self.ws.numel(), st,
+                                                        ctypes.c_void_p(self.gw_ready.cuda_event)))
         if self.gw16 is not None:
             self.bucket.weight_view.copy_(self.gw16)
-        self.bucket.all_reduce_async()
+            self.bucket.all_reduce_async()
+        else:
+            self.bucket.all_reduce_async(after=self.gw_ready)
         if cfg.softmax_mask:
             cabi.check(L.tvdcn_b200_mask_softmax_backward(cabi.F32, b, cfg.mask_groups, cfg.taps, sp, vp(self.gmask),
                                                           vp(self.mask), vp(self.glogits), st))
@@ -675,6 +682,27 @@ def batch_total(batch: int, device, world: int) -> int:
     return int(t.item())
 
 
+def allreduce_overlap(step, device):
+    """One diagnostic step (outside the timed regions): where the all-reduce of the weight gradients runs relative
+    to the backward pass, from CUDA events.  Times in ms since the start of the step."""
+    bucket = step.bucket
+    torch.cuda.synchronize()
+    t0, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    bucket.timing = []
+    t0.record()
+    step()
+    t_end.record()
+    torch.cuda.synchronize()
+    ev = bucket.timing
+    bucket.timing = None
+    if not ev:
+        return None
+    return {'allreduce_start_ms': t0.elapsed_time(ev[0]), 'allreduce_end_ms': t0.elapsed_time(ev[1]),
+            'step_end_ms': t0.elapsed_time(t_end),
+            'note': 'the exchange starts when the weight-gradient kernel finishes on the second stream and ends '
+                    'before the step does: it runs under the scatter kernel'}
+
+
 def check_reduced_gradient(cfg: Config, step, ts_global, device, world: int, rank: int):
     """Outside every timed region: the all-reduced [grad_weight | grad_bias] must equal (a) the sum of the ranks'
     own buckets and (b), on rank 0, the gradient one GPU computes for the whole global batch.  Returns the two
@@ -687,7 +715,7 @@ def check_reduced_gradient(cfg: Config, step, ts_global, device, world: int, ran
     reduced = bucket.flat.clone()
     # (a) local buckets: the same step with the exchange switched off
     saved = bucket.all_reduce_async
-    bucket.all_reduce_async = lambda: None
+    bucket.all_reduce_async = lambda *a, **k: None
     step()
     torch.cuda.synchronize()
     bucket.all_reduce_async = saved
@@ -700,7 +728,7 @@ def check_reduced_gradient(cfg: Config, step, ts_global, device, world: int, ran
     err_one = None
     if rank == 0 and ts_global is not None:
         solo = GradBucket(ts_global['w'].shape, cfg.cout, dtype=torch.float32, device=device)
-        solo.all_reduce_async = lambda: None     # rank 0 alone: no collective
+        solo.all_reduce_async = lambda *a, **k: None     # rank 0 alone: no collective
         one = DeviceStep(cfg, ts_global, 'fp32', device, solo)
         one()
         torch.cuda.synchronize()
@@ -779,9 +807,10 @@ def main():
 
     head, step = measure_mode(cfg, args.config, args.mode, ts, batch, device, bucket, world, barrier, args, L, local,
                               not args.no_e2e)
-    grad_check = None
+    grad_check, overlap = None, None
     if world > 1 and args.mode == 'fp32':
         grad_check = check_reduced_gradient(cfg, step, ts_global, device, world, rank)
+        overlap = allreduce_overlap(step, device)
     del step
     modes = {}
     other = 'bf16' if args.mode == 'fp32' else 'fp32'
@@ -830,7 +859,7 @@ def main():
             'kernels': head['kernels'], 'roofline': head['roofline'], 'cpu_baseline': base,
             'reference_cuda': ref_cuda, 'e2e': head['e2e'], 'operator_step_ms': head['operator_step_ms'],
             'gpu_launches': head['gpu_launches'], 'clocks': head['clocks'],
-            'modes': modes, 'weak': weak, 'grad_check': grad_check,
+            'modes': modes, 'weak': weak, 'grad_check': grad_check, 'allreduce_overlap': overlap,
         }
         emit(json.dumps(line))
     if world > 1:

@@ -176,6 +176,21 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p,
                                     void *workspace, size_t workspace_bytes,
                                     void *cuda_stream);
 
+/* The same call with one more argument for data-parallel training: `weight_grad_ready`, a cudaEvent_t the caller
+ * owns (or NULL), is recorded as soon as grad_weight and grad_bias hold their final values -- on the library's
+ * second stream when it is in use, well before the input / offset / mask gradients are done -- so that the
+ * all-reduce of the weight gradients can start under the rest of the backward pass.  No counterpart in the
+ * reference (its backward, tvdcn/csrc/ops/cuda/deform_conv2d_kernel.cpp:387-642, has no streams and no
+ * multi-GPU path). */
+int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p,
+                                       const void *grad_output,
+                                       const void *input, const void *weight,
+                                       const void *offset, const void *mask,
+                                       void *grad_input, void *grad_weight,
+                                       void *grad_offset, void *grad_mask, void *grad_bias,
+                                       void *workspace, size_t workspace_bytes,
+                                       void *cuda_stream, void *weight_grad_ready);
+
 /*
  * Softmax over the `taps` kernel points of each mask group:
  *   mask viewed as [batch, mask_groups, taps, spatial], normalised along taps.

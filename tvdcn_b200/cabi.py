@@ -53,6 +53,8 @@ def lib() -> C.CDLL:
         L.tvdcn_b200_deform_conv_forward.restype = C.c_int
         L.tvdcn_b200_deform_conv_backward.argtypes = [pp] + [vp] * 11 + [sz, vp]
         L.tvdcn_b200_deform_conv_backward.restype = C.c_int
+        L.tvdcn_b200_deform_conv_backward_ex.argtypes = [pp] + [vp] * 11 + [sz, vp, vp]
+        L.tvdcn_b200_deform_conv_backward_ex.restype = C.c_int
         L.tvdcn_b200_mask_softmax_forward.argtypes = [i32, i64, i64, i64, i64, vp, vp, vp]
         L.tvdcn_b200_mask_softmax_forward.restype = C.c_int
         L.tvdcn_b200_mask_softmax_backward.argtypes = [i32, i64, i64, i64, i64, vp, vp, vp, vp]

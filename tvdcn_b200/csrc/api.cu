@@ -386,7 +386,11 @@ static SideStream *side_stream() {
     SideStream &s = per_device[dev];
     if (!s.tried) {
         s.tried = true;
-        if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        // highest priority: the weight-gradient CTAs take the SMs the scatter kernel frees first, so the weight
+        // gradient is complete early in the call and its all-reduce can run under the rest of the scatter
+        int least = 0, greatest = 0;
+        (void)cudaDeviceGetStreamPriorityRange(&least, &greatest);
+        if (cudaStreamCreateWithPriority(&s.stream, cudaStreamNonBlocking, greatest) != cudaSuccess ||
             cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
             cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
             s.stream = nullptr;
@@ -400,6 +404,16 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
                                     const void *weight, const void *offset, const void *mask, void *grad_input,
                                     void *grad_weight, void *grad_offset, void *grad_mask, void *grad_bias,
                                     void *workspace, size_t workspace_bytes, void *cuda_stream) {
+    return tvdcn_b200_deform_conv_backward_ex(p, grad_output, input, weight, offset, mask, grad_input, grad_weight,
+                                              grad_offset, grad_mask, grad_bias, workspace, workspace_bytes,
+                                              cuda_stream, nullptr);
+}
+
+int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_output, const void *input,
+                                       const void *weight, const void *offset, const void *mask, void *grad_input,
+                                       void *grad_weight, void *grad_offset, void *grad_mask, void *grad_bias,
+                                       void *workspace, size_t workspace_bytes, void *cuda_stream,
+                                       void *weight_grad_ready) {
     int rc = check_problem(p);
     if (rc) return rc;
     rc = check_sizes(p);
@@ -416,6 +430,7 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
     if (p->batch == 0) {
         if (grad_weight) CUDA_TRY(cudaMemsetAsync(grad_weight, 0, n_w * es, stream));
         if (grad_bias) CUDA_TRY(cudaMemsetAsync(grad_bias, 0, (size_t)p->out_channels * as, stream));
+        if (weight_grad_ready) CUDA_TRY(cudaEventRecord((cudaEvent_t)weight_grad_ready, stream));
         return TVDCN_OK;  // empty batch: the sums over the batch are zero, empty tensors may be NULL
     }
     if (grad_output == nullptr || input == nullptr || weight == nullptr)
@@ -513,11 +528,17 @@ int tvdcn_b200_deform_conv_backward(const tvdcn_problem *p, const void *grad_out
             CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cs, g.S, grad_bias, stream));
         (void)n_dense;
     }
+    // grad_weight / grad_bias are final on the side stream already when they accumulate in place (f32 data)
+    const bool gw_in_place = !(gw_acc && pl.gw_acc != NO_BUF);
     if (side != nullptr) {  // join
+        if (weight_grad_ready && gw_in_place)
+            CUDA_TRY(cudaEventRecord((cudaEvent_t)weight_grad_ready, side->stream));
         CUDA_TRY(cudaEventRecord(side->join, side->stream));
         CUDA_TRY(cudaStreamWaitEvent(stream, side->join, 0));
     }
     if (gw_acc && pl.gw_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(dt, gw_acc, grad_weight, n_w, stream));
+    if (weight_grad_ready && !(side != nullptr && gw_in_place))
+        CUDA_TRY(cudaEventRecord((cudaEvent_t)weight_grad_ready, stream));
     if (goff_acc && pl.goff_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(aux, goff_acc, grad_offset, n_off, stream));
     if (gmask_acc && pl.gmask_acc != NO_BUF)
         CUDA_TRY(launch_cast_from_acc(aux, gmask_acc, grad_mask, n_mask, stream));

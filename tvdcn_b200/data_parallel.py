@@ -55,15 +55,26 @@ class GradBucket:
         self._work = None
         self._event = None
         self._side = torch.cuda.Stream(device=device) if self.flat.is_cuda else None
+        self.timing = None      # set to [] to have the next all_reduce_async bracket the exchange with timing events
 
-    def all_reduce_async(self) -> None:
-        """Start the SUM all-reduce; on CUDA it is ordered after the current stream's work so far."""
+    def all_reduce_async(self, after: Optional["torch.cuda.Event"] = None) -> None:
+        """Start the SUM all-reduce.  On CUDA it is ordered after the current stream's work so far, or, when
+        ``after`` is given, only after that event (the "weight gradient ready" event of the backward call), so
+        that it runs under the rest of the backward pass."""
         if not dist.is_initialized() or dist.get_world_size(self.group) == 1:
             return
         if self._side is not None:
-            self._side.wait_stream(torch.cuda.current_stream(self.flat.device))
+            if after is not None:
+                self._side.wait_event(after)
+            else:
+                self._side.wait_stream(torch.cuda.current_stream(self.flat.device))
             with torch.cuda.stream(self._side):
+                if self.timing is not None:      # [start, end] events of this exchange, for overlap diagnostics
+                    self.timing = [torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)]
+                    self.timing[0].record(self._side)
                 dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group)
+                if self.timing is not None:
+                    self.timing[1].record(self._side)
                 self._event = torch.cuda.Event()
                 self._event.record(self._side)
         else:
