@@ -396,32 +396,51 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
         const PosInfo<DIM> pa = decode_position<DIM>(g, m0 + q * 32 + lane);
         const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
         const int64_t base = ((int64_t)pa.b * g.Cd + (int64_t)grp * g.cdg) * g.P + pa.p;
-        for (int u = part; u < g.cdg / 16; u += SC_LOAD_WARPS / 4) {
-            const int d0 = u * 16;
-            uint32_t hi[8];
+        // two units (32 loads) in flight per thread: the tile is read once from DRAM, its latency is what counts
+        const int n_units_a = g.cdg / 16;
+        for (int u0 = part; u0 < n_units_a; u0 += 2 * (SC_LOAD_WARPS / 4)) {
+            const int u1 = u0 + SC_LOAD_WARPS / 4;
+            const bool two = u1 < n_units_a;
             if constexpr (SPLIT) {
-                const float *src = reinterpret_cast<const float *>(P.dense) + base + (int64_t)d0 * g.P;
-                float v[16];
+                const float *src0 = reinterpret_cast<const float *>(P.dense) + base + (int64_t)(u0 * 16) * g.P;
+                const float *src1 = reinterpret_cast<const float *>(P.dense) + base + (int64_t)(u1 * 16) * g.P;
+                float v[2][16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = pa.valid ? __ldg(src + (int64_t)i * g.P) : 0.f;
-                uint32_t lo[8];
+                for (int i = 0; i < 16; ++i) v[0][i] = pa.valid ? __ldg(src0 + (int64_t)i * g.P) : 0.f;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    hi[i] = pack2(v[2 * i], v[2 * i + 1], __nv_bfloat16());
-                    const float l0 = v[2 * i] - __uint_as_float(hi[i] << 16);
-                    const float l1 = v[2 * i + 1] - __uint_as_float(hi[i] & 0xffff0000u);
-                    lo[i] = pack2(l0, l1, __nv_bfloat16());
+                for (int i = 0; i < 16; ++i) v[1][i] = (pa.valid && two) ? __ldg(src1 + (int64_t)i * g.P) : 0.f;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (h == 1 && !two) break;
+                    const int d0 = (h == 0 ? u0 : u1) * 16;
+                    uint32_t hi[8], lo[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        hi[i] = pack2(v[h][2 * i], v[h][2 * i + 1], __nv_bfloat16());
+                        const float l0 = v[h][2 * i] - __uint_as_float(hi[i] << 16);
+                        const float l1 = v[h][2 * i + 1] - __uint_as_float(hi[i] & 0xffff0000u);
+                        lo[i] = pack2(l0, l1, __nv_bfloat16());
+                    }
+                    ptx::tmem_st_32x8(t_lane + (uint32_t)(d0 / 2), hi);
+                    ptx::tmem_st_32x8(t_lane + (uint32_t)(a_cols + d0 / 2), lo);
                 }
-                ptx::tmem_st_32x8(t_lane + (uint32_t)(d0 / 2), hi);
-                ptx::tmem_st_32x8(t_lane + (uint32_t)(a_cols + d0 / 2), lo);
             } else {
-                const uint16_t *src = reinterpret_cast<const uint16_t *>(P.dense) + base + (int64_t)d0 * g.P;
-                uint32_t v[16];
+                const uint16_t *src0 = reinterpret_cast<const uint16_t *>(P.dense) + base + (int64_t)(u0 * 16) * g.P;
+                const uint16_t *src1 = reinterpret_cast<const uint16_t *>(P.dense) + base + (int64_t)(u1 * 16) * g.P;
+                uint32_t v[2][16];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[i] = pa.valid ? (uint32_t)__ldg(src + (int64_t)i * g.P) : 0u;
+                for (int i = 0; i < 16; ++i) v[0][i] = pa.valid ? (uint32_t)__ldg(src0 + (int64_t)i * g.P) : 0u;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) hi[i] = v[2 * i] | (v[2 * i + 1] << 16);
-                ptx::tmem_st_32x8(t_lane + (uint32_t)(d0 / 2), hi);
+                for (int i = 0; i < 16; ++i) v[1][i] = (pa.valid && two) ? (uint32_t)__ldg(src1 + (int64_t)i * g.P) : 0u;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    if (h == 1 && !two) break;
+                    const int d0 = (h == 0 ? u0 : u1) * 16;
+                    uint32_t hi[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) hi[i] = v[h][2 * i] | (v[h][2 * i + 1] << 16);
+                    ptx::tmem_st_32x8(t_lane + (uint32_t)(d0 / 2), hi);
+                }
             }
         }
         ptx::tmem_st_wait();
@@ -434,8 +453,8 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
     if (warp < SC_WORK_WARPS) {
         if (warp < SC_STORE_WARPS) {
             // -------------------------------------------------------------- store warps: TMEM -> shared
+            load_dense();                      // with the launch allocation, before registers are handed over
             ptx::reg_dec<SC_REGS_STORE>();
-            load_dense();
             const int q = warp;
             const int row = q * 32 + lane;
             const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + row);
@@ -514,8 +533,8 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
             }
         } else {
             // -------------------------------------------------------------- gather warps
-            ptx::reg_inc<SC_REGS_WORK>();
             if (warp < SC_LOAD_WARPS) load_dense();
+            ptx::reg_inc<SC_REGS_WORK>();
             // An 8-lane group walks its span of the pixel-grouped entry list four entries at a time; lane l8 owns
             // channels 4 l8 .. 4 l8 + 3 of the slab.  The next four entries (and their image rows) are fetched
             // while the current four are processed.
