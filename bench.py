@@ -328,14 +328,26 @@ def peaks():
 
 def known_traffic(kernel: str, config: int, mode: str):
     """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
-    under profiles/ (config2_tensor_kernels.md); None where no capture exists."""
+    under profiles/; None where no capture exists.  The figures are for the configuration's full batch on one GPU."""
     table = {
-        'dcn_fwd_tc/cfg2/bf16': 85.16e6 + 21.68e6,
-        'dcn_dgrad_tc/cfg2/bf16': 329.76e6 + 104.70e6,
-        'dcn_wgrad_tc/cfg2/bf16': 137.71e6 + 3.80e6,
-        'dcn_fwd_tc/cfg2/fp32': 138.19e6 + 65.25e6,
-        'dcn_dgrad_tc/cfg2/fp32': 485.68e6 + 115.06e6,
-        'dcn_wgrad_tc/cfg2/fp32': 245.74e6 + 7.91e6,
+        # config 2: full-size launches (profiles/config2_tensor_kernels.md)
+        'dcn_fwd_tc/cfg2/bf16': 85.16e6 + 22.05e6,
+        'dcn_dgrad_tc/cfg2/bf16': 330.7e6 + 103.3e6,
+        'dcn_wgrad_tc/cfg2/bf16': 137.8e6 + 3.97e6,
+        'dcn_fwd_tc/cfg2/fp32': 137.8e6 + 65.84e6,
+        'dcn_dgrad_tc/cfg2/fp32': 486.7e6 + 115.9e6,
+        'dcn_wgrad_tc/cfg2/fp32': 246.1e6 + 7.99e6,
+        # configs 3-5: captured on a cut batch (profiles/config3_config4_config5_tensor_kernels.md) and scaled to
+        # the full batch by the images processed -- tiles are independent, traffic grows in proportion
+        'dcn_fwd_tc/cfg3/fp32': (73.8e6 + 29.55e6) * 8,
+        'dcn_dgrad_tc/cfg3/fp32': (214.6e6 + 44.33e6) * 8,
+        'dcn_wgrad_tc/cfg3/fp32': (141.5e6 + 4.76e6) * 8,
+        'dcn_fwd_tc/cfg4/fp32': (70.56e6 + 7.59e6) * 4,
+        'dcn_dgrad_tc/cfg4/fp32': (229.9e6 + 61.28e6) * 4,
+        'dcn_wgrad_tc/cfg4/fp32': (95.28e6 + 3.93e6) * 4,
+        'dcn_fwd_tc/cfg5/fp32': (40.98e6 + 0.15e6) * 4,
+        'dcn_dgrad_tc/cfg5/fp32': (58.56e6 + 0.50e6 + 63.9e6 + 1.27e6) / 2 * 4,   # two launches per step, mean
+        'dcn_wgrad_tc/cfg5/fp32': (57.76e6 + 0.70e6) * 4,
     }
     return table.get(f'{kernel}/cfg{config}/{mode}')
 
