@@ -601,20 +601,23 @@ def dominant_roofline(cfg: Config, kernels: dict, batch: int, config_index: int,
         return None
     dom = max(kernels, key=lambda k: kernels[k]['ms_per_step'])
     ms = kernels[dom]['ms_per_launch']
+    traffic = known_traffic(dom, config_index, mode)
+    if traffic is not None:
+        traffic *= batch / cfg.batch      # the captures are for the whole batch; traffic grows with the images
     if cfg.bound == 'tensor' and dom in gemm_like:
         ach = cfg.flops_per_pass(batch) / (ms / 1e3) / 1e12
         # a kernel of about a millisecond timed by events between other kernels: the burst figure is the denominator
         peak = pk['tflops_burst']
         return {'kernel': dom, 'bound': 'tensor', 'achieved': ach, 'peak': peak, 'unit': 'TFLOP/s',
                 'frac': ach / peak, 'frac_of_sustained': ach / pk['tflops_sustained'],
-                'traffic': known_traffic(dom, config_index, mode),
+                'traffic': traffic,
                 'peak_source': pk['source'] + ' bf16 dense, burst (of measured)',
                 'note': 'algorithmic FLOPs of one GEMM pass (2*Cout*Cin/g*taps*N*P) / CUDA-event time'}
     # share of the step's algorithmic bytes: a GEMM-shaped kernel touches about a third of them
     share = cfg.algorithmic_bytes(batch) / 3 if dom in gemm_like else cfg.algorithmic_bytes(batch)
     ach = share / (ms / 1e3) / 1e9
     return {'kernel': dom, 'bound': 'hbm', 'achieved': ach, 'peak': pk['hbm_gbs'], 'unit': 'GB/s',
-            'frac': ach / pk['hbm_gbs'], 'traffic': known_traffic(dom, config_index, mode),
+            'frac': ach / pk['hbm_gbs'], 'traffic': traffic,
             'peak_source': pk['source'] + ' copy bandwidth (of measured)'}
 
 
