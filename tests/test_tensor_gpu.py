@@ -174,3 +174,21 @@ def test_backward_reuses_the_forward_staging(dtype):
         assert torch.isfinite(a.float()).all()
         assert nerr(a, b) < tol
     assert L.tvdcn_b200_device_status() == 0
+
+
+def test_misaligned_16bit_grad_output_still_computes():
+    """A contiguous bf16 grad_output whose storage offset leaves it off a 16-byte boundary cannot be read by TMA:
+    the weight gradient must fall back to the SIMT kernel instead of failing the whole backward call."""
+    case = Case('misaligned', 2, False, 2, 64, 64, (8, 8), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 1, 1, True, 1.0)
+    x, w, off, mask, bias, go = make_inputs(case, seed=47)
+    dev = [x.bfloat16().cuda(), w.bfloat16().cuda(), off.float().cuda(), mask.float().cuda(), bias.float().cuda()]
+    go16 = go.bfloat16()
+    base = torch.empty(go16.numel() + 1, dtype=torch.bfloat16, device='cuda')
+    go_dev = base[1:].view(go16.shape)
+    go_dev.copy_(go16)
+    assert go_dev.data_ptr() % 16 != 0 and go_dev.is_contiguous()
+    ref = run_oracle(case, *(t.double().cpu() for t in dev), go16.double())
+    names, got = kernels_launched(lambda: cases.run_cabi(case, *dev, go_dev))
+    assert names.get('sample_wgrad', 0) == 1 and 'dcn_wgrad_tc' not in names, names
+    assert names.get('dcn_dgrad_tc', 0) == 1, names
+    cases.assert_parity(got, ref, 2e-2, case.name)

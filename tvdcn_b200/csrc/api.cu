@@ -466,8 +466,13 @@ int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_
     if (goff_acc) CUDA_TRY(cudaMemsetAsync(goff_acc, 0, n_off * acs, stream));
     if (gmask_acc) CUDA_TRY(cudaMemsetAsync(gmask_acc, 0, n_mask * acs, stream));
 
+    // The weight-gradient kernel reads 16-bit dense tensors by TMA straight from the caller's pointer, which must
+    // then sit on a 16-byte boundary (a tensor view with a storage offset may not): the SIMT kernel takes over.
+    const void *dense_for_w = p->transposed ? input : grad_output;
+    const bool tc_sw = pl.tc_sw && (p->dtype == TVDCN_F32 || (reinterpret_cast<uintptr_t>(dense_for_w) & 15) == 0);
+
     // fork: weight gradient + bias sum on the side stream when both sides run on the tensor cores
-    SideStream *side = (pl.tc_sw && gw_acc && (pl.tc_gs || pl.tc_sg)) ? side_stream() : nullptr;
+    SideStream *side = (tc_sw && gw_acc && (pl.tc_gs || pl.tc_sg)) ? side_stream() : nullptr;
     cudaStream_t wstream = stream;
     if (side != nullptr) {
         CUDA_TRY(stage_image(p, g, pl, p->transposed ? grad_output : input, ws, stream));
@@ -495,7 +500,7 @@ int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_
         }
         if (side != nullptr) {
             // already queued beside the scatter kernel
-        } else if (gw_acc && pl.tc_sw)
+        } else if (gw_acc && tc_sw)
             CUDA_TRY(run_sample_wgrad_tc(p, g, pl, grad_output, input, offset, mask, gw_acc, ws, stream));
         else if (gw_acc)
             CUDA_TRY(launch_sample_wgrad(g, dt, aux, grad_output, input, offset, mask, gw_acc, stream));
@@ -520,7 +525,7 @@ int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_
             CUDA_TRY(launch_sample_gemm(g, dt, aux, grad_output, weight, offset, mask, nullptr, grad_input, stream));
         if (side != nullptr) {
             // already queued beside the other kernels
-        } else if (gw_acc && pl.tc_sw)
+        } else if (gw_acc && tc_sw)
             CUDA_TRY(run_sample_wgrad_tc(p, g, pl, input, grad_output, offset, mask, gw_acc, ws, stream));
         else if (gw_acc)
             CUDA_TRY(launch_sample_wgrad(g, dt, aux, input, grad_output, offset, mask, gw_acc, stream));

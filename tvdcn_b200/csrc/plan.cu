@@ -26,6 +26,7 @@ const char *tc_common(const tvdcn_problem *p, const GeoHost &g) {
     if (csg % 64 != 0) return "sampled channels per group must be a multiple of 64";
     if (cdg % 64 != 0) return "dense channels per group must be a multiple of 64";
     if (g.K > 512) return "more than 512 kernel taps (the tensor-core kernels tabulate tap coordinates)";
+    if (g.B > 65535) return "batch above 65535 (the layout staging kernels put the batch in gridDim.z)";
     if (g.og > 0 && (g.Cs / g.og) % 64 != 0) return "channels per offset group must be a multiple of 64";
     if (g.mg > 0 && (g.Cs / g.mg) % 64 != 0) return "channels per mask group must be a multiple of 64";
     if (((long long)g.B * g.S + 1) * g.Cs >= (1LL << 31) || (long long)g.B * g.P >= (1LL << 31))
