@@ -11,8 +11,8 @@
 // (tcgen05.ld: lane = position) and store NCHW with the bias added, so the reference's output_buf
 // transpose and bias pass (tvdcn/csrc/ops/cuda/deform_conv2d_kernel.cpp:371-380) are gone too.
 //
-// Warp roles (704 threads): warps 0-15 producers + epilogue, warp 16 MMA issue + TMEM owner, warp 17 TMA,
-// warps 18-21 planners (sampling coordinates -> plan entries + L1 prefetch, a few chunks ahead).
+// Warp roles (768 threads): warps 0-15 producers + epilogue, warps 16-19 planners, warp 20 MMA issue + TMEM owner,
+// warp 21 TMA, warps 22-23 idle.  The planners turn sampling coordinates into plan entries a few chunks ahead.
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -54,7 +54,18 @@ __host__ __device__ constexpr int producer_groups_of(int mode) {
 }
 constexpr int PLANNER_WARPS = 4;                  // one planner thread per tile position
 constexpr int PLAN_BUFS = 4;
-constexpr int FWD_THREADS = PRODUCERS + 64 + PLANNER_WARPS * 32;
+// Warps: 0-15 producers (four warpgroups), 16-19 planners, 20 MMA, 21 TMA, 22-23 idle (they complete the last
+// warpgroup).  The warpgroups re-divide the registers at kernel start (launch: 80 each, 6 x 80 = 480): the
+// producers, who keep the gathers of several positions in flight, take FWD_REGS_PRODUCER, the planners and the
+// MMA / TMA warpgroup give up what that costs: 4 x 104 + 40 + 24 = 480.
+constexpr int MMA_WARP = PRODUCER_WARPS + PLANNER_WARPS;
+constexpr int TMA_WARP = MMA_WARP + 1;
+constexpr int FWD_THREADS = (TMA_WARP + 3) * 32;
+static_assert(FWD_THREADS == 768, "six warpgroups");
+constexpr int FWD_REGS_PRODUCER = 104, FWD_REGS_PLANNER = 40, FWD_REGS_ISSUE = 24;
+#ifndef TVDCN_FWD_IB
+#define TVDCN_FWD_IB 4
+#endif
 constexpr int FWD_MAX_TAPS = 512;                 // taps whose kernel coordinates a CTA tabulates (more: SIMT kernels)
 
 template <int DIM, int MODE>
@@ -128,11 +139,11 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
         }
         ptx::fence_mbar_init();
     }
-    if (warp == PRODUCER_WARPS + 1 && lane == 0) {
+    if (warp == TMA_WARP && lane == 0) {
         ptx::prefetch_tmap(&tmap_hi);
         if (SPLIT) ptx::prefetch_tmap(&tmap_lo);
     }
-    if (warp == PRODUCER_WARPS) {
+    if (warp == MMA_WARP) {
         ptx::tmem_alloc(tmem_slot, ncols);
         ptx::tmem_relinquish();
     }
@@ -150,6 +161,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
 
     if (warp < PRODUCER_WARPS) {
         // ------------------------------------------------------------------ producers
+        ptx::reg_inc<FWD_REGS_PRODUCER>();
         const int t = threadIdx.x;
         // position this thread stores in the epilogue (TMEM lane of its warp)
         const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + (warp & 3) * 32 + lane);
@@ -173,7 +185,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
             if (!ok) break;
             uint8_t *a_hi = sA + (size_t)s * a_stage_bytes;
             const uint32_t c16 = (uint32_t)chunk_chan0(j) * ESZ / 16u;
-            produce_tiles<NC, MODE, GROUP_THREADS, 2>(a_hi, a_hi + A_TILE_BYTES, 0u, TILE_POS, TILE_POS, img16, &c16,
+            produce_tiles<NC, MODE, GROUP_THREADS, (NC >= 8 ? 2 : TVDCN_FWD_IB)>(a_hi, a_hi + A_TILE_BYTES, 0u, TILE_POS, TILE_POS, img16, &c16,
                                                    plan + pbuf * TILE_POS * NC, tg);
             ptx::fence_proxy_async_smem();
             __syncwarp();
@@ -220,8 +232,9 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
                 }
             }
         }
-    } else if (warp == PRODUCER_WARPS) {
+    } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issue
+        ptx::reg_dec<FWD_REGS_ISSUE>();
         if (lane == 0) {
             const uint32_t idesc = ptx::instr_desc_f16(MODE == TC_F16 ? 0 : 1, TILE_POS, BN, 0, 0);
             bool ok = true;
@@ -260,8 +273,9 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
             if (ok) ptx::mma_commit(accum);
         }
         __syncwarp();
-    } else if (warp == PRODUCER_WARPS + 1) {
+    } else if (warp == TMA_WARP) {
         // ------------------------------------------------------------------ TMA: weight tiles
+        ptx::reg_dec<FWD_REGS_ISSUE>();
         if (lane == 0) {
             int s = 0, tap = 0, cc = 0, last_s = -1;
             uint32_t e_phase = 1, last_phase = 0;
@@ -291,11 +305,14 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
         __syncwarp();
     }
 
-    if (warp >= PRODUCER_WARPS + 2) {
+    if (warp > TMA_WARP) ptx::reg_dec<FWD_REGS_ISSUE>();   // the two idle warps of the last warpgroup
+
+    if (warp >= PRODUCER_WARPS && warp < MMA_WARP) {
         // ------------------------------------------------------------------ planners: one thread per position
+        ptx::reg_dec<FWD_REGS_PLANNER>();
         // run ahead of the producers: coordinates -> plan entries, and an L1 prefetch of every corner row so
         // that the producers' gathers hit L1
-        const int t = threadIdx.x - (PRODUCERS + 64);
+        const int t = threadIdx.x - PRODUCERS;
         const PosInfo<DIM> pi = decode_position<DIM>(g, m0 + t);
         const bool deformable = P.offset != nullptr;
         const uint32_t row_scale = (uint32_t)g.Cs * ESZ / 16u;
@@ -390,7 +407,7 @@ dcn_fwd_tc_kernel(const FwdParams<DIM> P, const __grid_constant__ CUtensorMap tm
 
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == PRODUCER_WARPS) ptx::tmem_dealloc(tmem_base, ncols);
+    if (warp == MMA_WARP) ptx::tmem_dealloc(tmem_base, ncols);
 }
 
 // ---- staging kernels ---------------------------------------------------------------------------------
