@@ -75,13 +75,11 @@ static_assert(SC_THREADS == 768, "six warpgroups");
 constexpr int SC_REGS_WORK = 96, SC_REGS_STORE = 56, SC_REGS_ISSUE = 40;
 constexpr int SC_GROUPS = SC_GATHER_WARPS * 4;                    // 8-lane groups walking the entry list
 constexpr int SC_SLAB = 32;                                       // channels per pass
-constexpr int SC_PLAN_SLACK = SC_GROUPS * 5 + 16;
+constexpr int SC_PLAN_SLACK = SC_GROUPS * 4 + 16;
 constexpr int SC_HASH = 2048;                                     // slots; >= entries of one unit
 constexpr uint32_t SC_NONE = 0xffffffffu;
 constexpr int SC_TMEM_COLS = 512;
-#ifndef SC_SLEEP_NS
-#define SC_SLEEP_NS 32
-#endif
+constexpr int SC_SLEEP_NS = 32;                                   // back-off of the long waits (64 to 512 measured equal)
 constexpr int SC_MAX_TAPS = 512;                                  // taps whose kernel coordinates a CTA tabulates
 
 // most taps per batch: 128 * tb * 2^dim entries must fit the hash table
@@ -118,31 +116,6 @@ struct TapGeometry {
     float mval;
 };
 
-template <int DIM>
-__device__ __forceinline__ TapGeometry<DIM> load_geometry(const Geo<DIM> &g, const PosInfo<DIM> &pi,
-                                                          const float *__restrict__ offset,
-                                                          const float *__restrict__ mask, int tap, int ogi, int mgi) {
-    TapGeometry<DIM> tg;
-    int tc[DIM];
-    tap_coords<DIM>(g, tap, tc);
-#pragma unroll
-    for (int a = 0; a < DIM; ++a) {
-        const int base = pi.base[a] + tc[a] * g.dil[a];
-        if (offset != nullptr) {
-            const float o = __ldg(offset + ((((int64_t)pi.b * g.og + ogi) * g.K + tap) * DIM + a) * (int64_t)g.P + pi.p);
-            const float pos = (float)base + o;
-            const float f = floorf(pos);
-            tg.fl[a] = (int)f;
-            tg.fr[a] = pos - f;
-        } else {
-            tg.fl[a] = base;
-            tg.fr[a] = 0.f;
-        }
-    }
-    tg.mval = mask != nullptr ? __ldg(mask + (((int64_t)pi.b * g.mg + mgi) * g.K + tap) * (int64_t)g.P + pi.p) : 1.f;
-    return tg;
-}
-
 // corner c of the 2^DIM cell: in the image?, pixel row of the channels-last image, interpolation weight
 template <int DIM>
 __device__ __forceinline__ void corner_of(const Geo<DIM> &g, const PosInfo<DIM> &pi, const TapGeometry<DIM> &tg,
@@ -176,8 +149,8 @@ __host__ __device__ inline ScLayout sc_layout(int dim, int mode, int tb, int b_s
     (void)parts;
     L.col_buf = (uint32_t)(TILE_POS * L.col_stride * 4);
     // three arrays (pixel offset; col index | dot slot << 16; weight) of max_entries + SC_PLAN_SLACK words -- room for
-    // the padding of the groups' spans, one unused word between the groups and the read-ahead of the last group --
-    // then one dot product per entry (+ a slot for the padding entries)
+    // the padding of the groups' spans and the read-ahead of the last group -- then one dot product per entry (+ a
+    // slot for the padding entries)
     L.plan_buf = (uint32_t)(3 * (L.max_entries + SC_PLAN_SLACK) * 4 + (L.max_entries + 4) * 4);
     uint32_t o = 0;
     o += (uint32_t)b_stages * L.b_stage;
@@ -232,8 +205,9 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
     uint64_t *plan_done = plan_full + 2; // [2] gather warps -> whoever turns the unit's dots into gradients / planners
     uint64_t *fin_done = plan_done + 2;  // [2] store warps -> planners: the unit's dots have been used
     int16_t *tap_tab = reinterpret_cast<int16_t *>(smem + L.taps);
-    // Entry e of the pixel-grouped list sits at word e + e / span of each array: the groups' spans start span + 1
-    // words apart, so that the four groups of a gather warp read four different banks.
+    // Entry e of the pixel-grouped list sits at word e of each array; a group's span is a multiple of four entries, so
+    // that a batch of four is one 16-byte read per array (each 8-lane group is a quarter-warp phase of its own: the
+    // four groups of a warp never meet in one bank access).
     const int plan_words = L.max_entries + SC_PLAN_SLACK;
     auto plan_px = [&](int pb) { return reinterpret_cast<uint32_t *>(smem + L.plan + (size_t)pb * L.plan_buf); };
     auto plan_meta = [&](int pb) { return plan_px(pb) + plan_words; };
@@ -563,9 +537,9 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                     break;
                 }
                 const int span = (int)n_entries[pb];     // entries per group, padded: a multiple of 4
-                const uint32_t *my_px = plan_px(pb) + gid * (span + 1);
-                const uint32_t *my_meta = plan_meta(pb) + gid * (span + 1);
-                const float *my_w = plan_w(pb) + gid * (span + 1);
+                const uint4 *my_px = reinterpret_cast<const uint4 *>(plan_px(pb) + gid * span);
+                const uint4 *my_meta = reinterpret_cast<const uint4 *>(plan_meta(pb) + gid * span);
+                const float4 *my_w = reinterpret_cast<const float4 *>(plan_w(pb) + gid * span);
                 float *p_dot = plan_dot(pb);
                 const float4 *colb = reinterpret_cast<const float4 *>(col + (size_t)cb * (L.col_buf / 4)) + l8;
                 const uint32_t chan = (uint32_t)(grp * g.csg + chunk * CHUNK_C + slab * SC_SLAB + l8 * 4);
@@ -576,8 +550,8 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
                 // pixel offsets of the four entries at `at`, and (for the coordinate gradients) their image rows
                 auto fetch_rows = [&](uint32_t (&px)[4], RAW (&R)[4], int at) {
-#pragma unroll
-                    for (int s = 0; s < 4; ++s) px[s] = my_px[at + s];
+                    const uint4 p4 = my_px[at >> 2];
+                    px[0] = p4.x; px[1] = p4.y; px[2] = p4.z; px[3] = p4.w;
                     if constexpr (COORD) {
 #pragma unroll
                         for (int s = 0; s < 4; ++s) R[s] = __ldg(reinterpret_cast<const RAW *>(img_c + px[s]));
@@ -597,13 +571,10 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                     }
                 };
                 auto process = [&](int at, const uint32_t (&pxs)[4], const RAW (&R)[4]) {
-                    uint32_t meta[4];
-                    float wt[4];
-#pragma unroll
-                    for (int s = 0; s < 4; ++s) {
-                        meta[s] = my_meta[at + s];
-                        wt[s] = my_w[at + s];
-                    }
+                    const uint4 m4 = my_meta[at >> 2];
+                    const float4 w4 = my_w[at >> 2];
+                    const uint32_t meta[4] = {m4.x, m4.y, m4.z, m4.w};
+                    const float wt[4] = {w4.x, w4.y, w4.z, w4.w};
                     float d[4];
 #pragma unroll
                     for (int s = 0; s < 4; ++s) {
@@ -778,34 +749,31 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
             if (pt == 0) n_entries[pb] = span;
             planner_barrier();
             phase(3);
-            // pass 2: every entry goes to (start of its pixel's run) + (its rank), counted in the padded layout
+            // pass 2: every entry goes to (start of its pixel's run) + (its rank)
             uint32_t *e_px = plan_px(pb);
             uint32_t *e_meta = plan_meta(pb);
             float *e_w = plan_w(pb);
-            const uint32_t magic = span > 0 ? (uint32_t)((0x100000000ull + span - 1) / span) : 0u;   // e / span for e < 2^16
 #pragma unroll
             for (int t = 0; t < TBM; ++t) {
 #pragma unroll
                 for (int c = 0; c < NC; ++c) {
                     const int i = t * NC + c;
                     if (rows[i] != SC_NONE) {
-                        const uint32_t e = cnt[slot[i]] + old[i];
-                        const uint32_t at = e + __umulhi(e, magic);
+                        const uint32_t at = cnt[slot[i]] + old[i];
                         e_px[at] = rows[i] * (uint32_t)g.Cs;
                         e_meta[at] = (colq_row + (uint32_t)(t * (SC_SLAB / 4))) | ((uint32_t)((pt * TB + t) * NC + c) << 16);
                         e_w[at] = wts[i];
                     }
                 }
             }
-            // padding entries up to the end of the last span, the unused word after each span and the words the
-            // read-ahead of the last group touches: all point at the row of zeros and add nothing
-            const uint32_t n_words = span * SC_GROUPS + SC_GROUPS + 8;
-            for (uint32_t i = total + total / (span > 0 ? span : 1) + pt; i < n_words; i += 128) {
+            // padding entries up to the end of the last span and the words the read-ahead of the last group touches:
+            // all point at the row of zeros and add nothing
+            const uint32_t n_words = span * SC_GROUPS + 8;
+            for (uint32_t i = total + pt; i < n_words; i += 128) {
                 e_px[i] = zrow;
                 e_meta[i] = (uint32_t)L.max_entries << 16;
                 e_w[i] = 0.f;
             }
-            if (pt < SC_GROUPS && span > 0) e_px[pt * (span + 1) + span] = zrow;
             phase(4);
             planner_barrier();
             phase(5);
