@@ -471,6 +471,14 @@ int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_
     const void *dense_for_w = p->transposed ? input : grad_output;
     const bool tc_sw = pl.tc_sw && (p->dtype == TVDCN_F32 || (reinterpret_cast<uintptr_t>(dense_for_w) & 15) == 0);
 
+    // the tensor-core weight-gradient kernel accumulates in a staged layout: convert right behind it
+    auto wgrad_tc = [&](const void *dense, const void *img, cudaStream_t st) -> cudaError_t {
+        cudaError_t e = run_sample_wgrad_tc(p, g, pl, dense, img, offset, mask, gw_acc, ws, st);
+        if (e != cudaSuccess) return e;
+        return launch_unpack_weight_grad((const float *)gw_acc, grad_weight, dt, g.groups, g.Cd / g.groups,
+                                         g.Cs / g.groups, g.K, st);
+    };
+
     // fork: weight gradient + bias sum on the side stream when both sides run on the tensor cores
     SideStream *side = (tc_sw && gw_acc && (pl.tc_gs || pl.tc_sg)) ? side_stream() : nullptr;
     cudaStream_t wstream = stream;
@@ -485,7 +493,7 @@ int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_
         // sampled image = input, dense = grad_output
         void *gi_acc = grad_input ? (pl.img_acc != NO_BUF ? (void *)(ws + pl.img_acc) : grad_input) : nullptr;
         if (side != nullptr) {
-            CUDA_TRY(run_sample_wgrad_tc(p, g, pl, grad_output, input, offset, mask, gw_acc, ws, wstream));
+            CUDA_TRY(wgrad_tc(grad_output, input, wstream));
             if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cd, g.P, grad_bias, wstream));
         }
         if (pl.tc_gs) {
@@ -501,7 +509,7 @@ int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_
         if (side != nullptr) {
             // already queued beside the scatter kernel
         } else if (gw_acc && tc_sw)
-            CUDA_TRY(run_sample_wgrad_tc(p, g, pl, grad_output, input, offset, mask, gw_acc, ws, stream));
+            CUDA_TRY(wgrad_tc(grad_output, input, stream));
         else if (gw_acc)
             CUDA_TRY(launch_sample_wgrad(g, dt, aux, grad_output, input, offset, mask, gw_acc, stream));
         if (grad_bias && side == nullptr)
@@ -510,7 +518,7 @@ int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_
     } else {
         // sampled image = grad_output, dense = input
         if (side != nullptr) {
-            CUDA_TRY(run_sample_wgrad_tc(p, g, pl, input, grad_output, offset, mask, gw_acc, ws, wstream));
+            CUDA_TRY(wgrad_tc(input, grad_output, wstream));
             if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cs, g.S, grad_bias, wstream));
         }
         if ((goff_acc || gmask_acc) && pl.tc_gs)
@@ -526,22 +534,22 @@ int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_
         if (side != nullptr) {
             // already queued beside the other kernels
         } else if (gw_acc && tc_sw)
-            CUDA_TRY(run_sample_wgrad_tc(p, g, pl, input, grad_output, offset, mask, gw_acc, ws, stream));
+            CUDA_TRY(wgrad_tc(input, grad_output, stream));
         else if (gw_acc)
             CUDA_TRY(launch_sample_wgrad(g, dt, aux, input, grad_output, offset, mask, gw_acc, stream));
         if (grad_bias && side == nullptr)
             CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cs, g.S, grad_bias, stream));
         (void)n_dense;
     }
-    // grad_weight / grad_bias are final on the side stream already when they accumulate in place (f32 data)
-    const bool gw_in_place = !(gw_acc && pl.gw_acc != NO_BUF);
+    // grad_weight / grad_bias are final on the side stream: the tensor-core kernel's staged sum is converted there
+    const bool gw_in_place = true;
     if (side != nullptr) {  // join
         if (weight_grad_ready && gw_in_place)
             CUDA_TRY(cudaEventRecord((cudaEvent_t)weight_grad_ready, side->stream));
         CUDA_TRY(cudaEventRecord(side->join, side->stream));
         CUDA_TRY(cudaStreamWaitEvent(stream, side->join, 0));
     }
-    if (gw_acc && pl.gw_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(dt, gw_acc, grad_weight, n_w, stream));
+    if (gw_acc && pl.gw_acc != NO_BUF && !tc_sw) CUDA_TRY(launch_cast_from_acc(dt, gw_acc, grad_weight, n_w, stream));
     if (weight_grad_ready && !(side != nullptr && gw_in_place))
         CUDA_TRY(cudaEventRecord((cudaEvent_t)weight_grad_ready, stream));
     if (goff_acc && pl.goff_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(aux, goff_acc, grad_offset, n_off, stream));

@@ -129,8 +129,10 @@ Plan plan_backward(const tvdcn_problem *p, bool want_input, bool want_weight, bo
     }
     if (is16(p->dtype)) {
         if (!p->transposed && want_input && !pl.tc_gs) pl.img_acc = b.take((size_t)g.B * g.Cs * g.S * sizeof(float));
-        if (want_weight) pl.gw_acc = b.take(nw * sizeof(float));
     }
+    // 16-bit data accumulates the weight gradient in f32; the tensor-core kernel accumulates (any data type) into
+    // a staged layout that a small kernel turns into the caller's afterwards
+    if (want_weight && (is16(p->dtype) || pl.tc_sw)) pl.gw_acc = b.take(nw * sizeof(float));
     if (is16(p->aux_dtype)) {
         if (want_offset) pl.goff_acc = b.take((size_t)g.B * g.og * g.K * g.dim * g.P * sizeof(float));
         if (want_mask) pl.gmask_acc = b.take((size_t)g.B * g.mg * g.K * g.P * sizeof(float));

@@ -20,7 +20,7 @@ struct Plan {
     size_t total = 0;              // workspace bytes
     // SIMT path: accumulation buffers for 16-bit outputs (byte offsets into the workspace)
     size_t img_acc = NO_BUF;       // sampled-image-shaped accumulator (grad_input / transposed output)
-    size_t gw_acc = NO_BUF;
+    size_t gw_acc = NO_BUF;        // f32 weight gradient: [Cd, csg, K] for the SIMT kernel, [g][tap][d'][s'] for the tensor-core one
     size_t goff_acc = NO_BUF;
     size_t gmask_acc = NO_BUF;
     // tensor path: staged copies
@@ -63,6 +63,9 @@ cudaError_t launch_from_channels_last_bias(const float *src, const float *bias, 
                                            int S, cudaStream_t stream);
 cudaError_t launch_pack_weight_kd(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
                                   void *lo, cudaStream_t stream);
+// staged weight gradient of the tensor-core kernel, [g][tap][d'][s'] f32 -> [Cd, csg, K] in the data type `dtype`
+cudaError_t launch_unpack_weight_grad(const float *staged, void *gw, int dtype, int groups, int cdg, int csg, int K,
+                                      cudaStream_t stream);
 cudaError_t launch_split_f32(const float *src, void *hi, void *lo, int64_t n, cudaStream_t stream);
 cudaError_t launch_to_channels_last(const void *src, void *dst, int B, int C, int S, int elem_bytes,
                                     cudaStream_t stream);

@@ -580,7 +580,7 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                     for (int s = 0; s < 4; ++s) {
                         const uint32_t px = pxs[s];
                         const bool change = px != cur;
-                        red_add_v4_if(change && cur != zrow && scatter, gimg_c + cur, acc.x, acc.y, acc.z, acc.w);
+                        red_add_v4_if(change && scatter, gimg_c + cur, acc.x, acc.y, acc.z, acc.w);
                         cur = px;
                         const float4 c4 = colb[meta[s] & 0xffffu];
                         const float w = wt[s];
@@ -612,7 +612,13 @@ dcn_dgrad_tc_kernel(const DgradParams<DIM> P, const __grid_constant__ CUtensorMa
                 };
                 RAW Ra[4], Rb[4];
                 uint32_t Pa[4], Pb[4];
-                if (span > 0) fetch_rows(Pa, Ra, 0);
+                if (span > 0) {
+                    fetch_rows(Pa, Ra, 0);
+                    // The running pixel starts as the first entry's: no flush before anything was summed.  Padding
+                    // entries (pixel offset zrow) only follow real ones, so inside the loop a flush never has
+                    // cur == zrow; the one after the loop may.
+                    cur = Pa[0];
+                }
                 for (int it = 0; it < span; it += 8) {
                     // the fetch one batch ahead may run up to 8 entries past the span: still inside the list's slack
                     fetch_rows(Pb, Rb, it + 4);

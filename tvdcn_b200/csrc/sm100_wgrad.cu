@@ -12,7 +12,9 @@
 //       that TMA loads directly (zero-filled past the end of an image);
 //   B = sampled tile [64 pos][64 channels] per column block, written by the producer warps in the same
 //       swizzled row = position layout as the forward kernel and consumed as an MN-major operand.
-// Position ranges are split over CTAs; partial results are added to gw (f32) with atomics.
+// Position ranges are split over CTAs; partial results are added with 16-byte vector reductions to a staged f32
+// copy of gw laid out [g][tap][d][s] (a thread holds 32 consecutive s of one d), which a small kernel then turns
+// into the caller's [Cd, Cs / groups, taps] tensor.
 //
 // Warp roles (704 threads): warps 0-15 producers + epilogue, in two groups that take alternate stages so that
 // one group's gathers are in flight while the other blends and stores; warp 16 MMA issue + TMEM owner;
@@ -31,7 +33,7 @@ struct WgradParams {
     const void *img_cl;
     const float *offset;
     const float *mask;
-    float *gw;               // [Cd, csg, K] f32, accumulated into
+    float *gw;               // staged weight gradient [g][tap][d'][s'] f32, accumulated into
     int *status;
     int stages;
     int chunks_per_tap;      // csg / 64
@@ -188,9 +190,16 @@ dcn_wgrad_tc_kernel(const WgradParams<DIM> P, const __grid_constant__ CUtensorMa
                     if (kt < sub_total && dl < g.cdg) {
                         const int tap = kt % g.K;
                         const int sl0 = (kt / g.K) * CHUNK_C + (col0 % 64);
-                        float *dst = P.gw + ((int64_t)(grp * g.cdg + dl) * g.csg + sl0) * g.K + tap;
+                        // staged layout [g][tap][d'][s']: this thread's 32 values are 128 contiguous bytes, added
+                        // with eight 16-byte reductions (the caller's [Cd, csg, K] layout would put every value in
+                        // a sector of its own)
+                        float *dst = P.gw + (((int64_t)grp * g.K + tap) * g.cdg + dl) * g.csg + sl0;
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) atomicAdd(dst + (int64_t)e * g.K, __uint_as_float(v[e]));
+                        for (int e = 0; e < 32; e += 4)
+                            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + e),
+                                         "f"(__uint_as_float(v[e])), "f"(__uint_as_float(v[e + 1])),
+                                         "f"(__uint_as_float(v[e + 2])), "f"(__uint_as_float(v[e + 3]))
+                                         : "memory");
                     }
                 }
             }
@@ -440,6 +449,46 @@ cudaError_t launch_sample_wgrad_tc(const GeoHost &h, int mode, const void *dense
     if (h.dim == 1) return run(std::integral_constant<int, 1>());
     if (h.dim == 2) return run(std::integral_constant<int, 2>());
     if (h.dim == 3) return run(std::integral_constant<int, 3>());
+    return cudaErrorInvalidValue;
+}
+
+namespace {
+// staged [g][tap][d'][s'] f32 -> the caller's [Cd, csg, K] in its data type
+template <typename TO>
+__global__ void __launch_bounds__(256) unpack_weight_grad_kernel(const float *__restrict__ staged, TO *__restrict__ gw,
+                                                                 int groups, int cdg, int csg, int K) {
+    // one block per (dense channel, 64 sampled channels): reads K rows of 64 floats, writes 64 * K contiguous values
+    extern __shared__ float tile[];   // [K][65]
+    const int d = blockIdx.x;                // grp * cdg + dl
+    const int grp = d / cdg, dl = d % cdg;
+    const int s0 = blockIdx.y * 64;
+    for (int i = threadIdx.x; i < K * 64; i += blockDim.x) {
+        const int tap = i / 64, sl = i % 64;
+        tile[tap * 65 + sl] = s0 + sl < csg ? staged[(((int64_t)grp * K + tap) * cdg + dl) * csg + s0 + sl] : 0.f;
+    }
+    __syncthreads();
+    TO *out = gw + ((int64_t)d * csg + s0) * K;
+    const int n = min(64, csg - s0) * K;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) store_acc(out, i, tile[(i % K) * 65 + i / K]);
+}
+}  // namespace
+
+cudaError_t launch_unpack_weight_grad(const float *staged, void *gw, int dtype, int groups, int cdg, int csg, int K,
+                                      cudaStream_t stream) {
+    dim3 grid((unsigned)(groups * cdg), (unsigned)((csg + 63) / 64));
+    const size_t smem = (size_t)K * 65 * sizeof(float);
+    auto run = [&](auto kern, auto *out) -> cudaError_t {
+        if (smem > 48 * 1024) {   // many taps: the tile needs the opt-in shared memory size
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+        }
+        LaunchScope scope("unpack_weight_grad", stream);
+        kern<<<grid, 256, smem, stream>>>(staged, out, groups, cdg, csg, K);
+        return cudaGetLastError();
+    };
+    if (dtype == DT_F32) return run(unpack_weight_grad_kernel<float>, (float *)gw);
+    if (dtype == DT_BF16) return run(unpack_weight_grad_kernel<__nv_bfloat16>, (__nv_bfloat16 *)gw);
+    if (dtype == DT_F16) return run(unpack_weight_grad_kernel<__half>, (__half *)gw);
     return cudaErrorInvalidValue;
 }
 
