@@ -331,12 +331,12 @@ def known_traffic(kernel: str, config: int, mode: str):
     under profiles/; None where no capture exists.  The figures are for the configuration's full batch on one GPU."""
     table = {
         # config 2: full-size launches (profiles/config2_tensor_kernels.md)
-        'dcn_fwd_tc/cfg2/bf16': 85.16e6 + 22.05e6,
-        'dcn_dgrad_tc/cfg2/bf16': 330.7e6 + 103.3e6,
-        'dcn_wgrad_tc/cfg2/bf16': 137.8e6 + 3.97e6,
-        'dcn_fwd_tc/cfg2/fp32': 137.8e6 + 65.84e6,
-        'dcn_dgrad_tc/cfg2/fp32': 486.7e6 + 115.9e6,
-        'dcn_wgrad_tc/cfg2/fp32': 246.1e6 + 7.99e6,
+        'dcn_fwd_tc/cfg2/bf16': 85.16e6 + 20.91e6,
+        'dcn_dgrad_tc/cfg2/bf16': 330.5e6 + 102.6e6,
+        'dcn_wgrad_tc/cfg2/bf16': 137.7e6 + 3.81e6,
+        'dcn_fwd_tc/cfg2/fp32': 137.8e6 + 64.83e6,
+        'dcn_dgrad_tc/cfg2/fp32': 487.1e6 + 116.9e6,
+        'dcn_wgrad_tc/cfg2/fp32': 243.0e6 + 7.46e6,
         # configs 3-5: captured on a cut batch (profiles/config3_config4_config5_tensor_kernels.md) and scaled to
         # the full batch by the images processed -- tiles are independent, traffic grows in proportion
         'dcn_fwd_tc/cfg3/fp32': (73.8e6 + 29.55e6) * 8,
