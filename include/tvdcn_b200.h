@@ -220,10 +220,15 @@ const char *tvdcn_b200_last_error(void);
  * device, returns the word (0 = no kernel reported a problem, -1 = the query itself failed) and clears it. */
 int tvdcn_b200_device_status(void);
 
-/* Device address of that status word on the current device (NULL if it cannot be found).  A caller that must not
- * synchronise can copy the word to pinned host memory behind its own work (cudaMemcpyAsync on its stream) and look
- * at the copy later; the PyTorch front end does that after every operator call and raises at the next one. */
+/* Device address of that status word on the current device (NULL if it cannot be found). */
 const int *tvdcn_b200_device_status_address(void);
+
+/* For a caller that must not synchronise: enqueues on `cuda_stream` a one-thread kernel that, if the status word is
+ * non-zero, stores it to `host_word_device_ptr` -- the device-side address (cudaHostGetDevicePointer) of an int in
+ * mapped pinned host memory that the caller zeroed.  The caller looks at the host int later.  A kernel store, not a
+ * copy: it does not queue behind the caller's own transfers on the copy engines.  The PyTorch front end does this
+ * after every operator call and raises at the next one.  No counterpart in the reference. */
+int tvdcn_b200_publish_status(int *host_word_device_ptr, void *cuda_stream);
 
 /* Self test of the bounded waits: launches, on `cuda_stream`, one small kernel that waits (at most `max_polls`
  * polls of about 20 microseconds, 1 <= max_polls <= 4096) on a barrier nothing ever arrives on, gives up and

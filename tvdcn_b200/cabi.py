@@ -67,6 +67,8 @@ def lib() -> C.CDLL:
         L.tvdcn_b200_engine_name.restype = C.c_char_p
         L.tvdcn_b200_device_status.restype = C.c_int
         L.tvdcn_b200_device_status_address.restype = vp
+        L.tvdcn_b200_publish_status.argtypes = [vp, vp]
+        L.tvdcn_b200_publish_status.restype = C.c_int
         L.tvdcn_b200_selftest_bounded_wait.argtypes = [C.c_int, vp]
         L.tvdcn_b200_selftest_bounded_wait.restype = C.c_int
         _proto_done = True

@@ -260,6 +260,13 @@ __global__ void bounded_wait_selftest_kernel(int *status, uint32_t max_polls) {
     if (!done && threadIdx.x == 0) atomicExch(status, 900);
 }
 
+// Copies a non-zero status word to host memory the device can write (mapped pinned memory): a store from a
+// kernel, so the copy engines, which may be busy with a caller's own large transfers, are not involved.
+__global__ void publish_status_kernel(const int *status, int *host_word) {
+    const int v = *status;
+    if (v != 0) *host_word = v;
+}
+
 }  // namespace tvdcn_b200
 
 using namespace tvdcn_b200;
@@ -645,6 +652,15 @@ int tvdcn_b200_device_status(void) {
 }
 
 const int *tvdcn_b200_device_status_address(void) { return device_status_word(); }
+
+int tvdcn_b200_publish_status(int *host_word_device_ptr, void *cuda_stream) {
+    if (host_word_device_ptr == nullptr) return fail(TVDCN_ERR_INVALID, "host_word_device_ptr is NULL");
+    const int *status = device_status_word();
+    if (status == nullptr) return fail(TVDCN_ERR_CUDA, "status word not found");
+    publish_status_kernel<<<1, 1, 0, (cudaStream_t)cuda_stream>>>(status, host_word_device_ptr);
+    CUDA_TRY(cudaGetLastError());
+    return TVDCN_OK;
+}
 
 uint64_t tvdcn_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

@@ -247,11 +247,13 @@ Call prepare(const Tensor &input, const Tensor &weight, const OptTensor &offset,
 
 // ---- status of the bounded waits, without a synchronisation per call --------------------------------------
 // The tensor-core kernels give up on a barrier wait that runs out and leave a code in a per-device word; their
-// outputs are then incomplete.  After every operator call the word is copied, behind the call's kernels on the same
-// stream, into one pinned host integer per device; the next operator call on that device looks at the copy first
-// and raises.  With TVDCN_B200_CHECK_STATUS=1 every call synchronises and raises itself.
+// outputs are then incomplete.  After every operator call a one-thread kernel, behind the call's kernels on the same
+// stream, stores a non-zero word into one mapped pinned host integer per device (a store, not a copy: a copy would
+// queue behind the caller's own transfers on the copy engines); the next operator call on that device looks at the
+// integer first and raises.  With TVDCN_B200_CHECK_STATUS=1 every call synchronises and raises itself.
 struct StatusWatch {
-    int *pinned = nullptr;
+    int *pinned = nullptr;       // host view of the mapped pinned word
+    int *pinned_dev = nullptr;   // the same word as the device addresses it
     bool tried = false;
 };
 StatusWatch &status_watch(int device) {
@@ -259,10 +261,14 @@ StatusWatch &status_watch(int device) {
     StatusWatch &w = per_device[device & 63];
     if (!w.tried) {
         w.tried = true;
-        if (cudaHostAlloc(reinterpret_cast<void **>(&w.pinned), sizeof(int), cudaHostAllocDefault) == cudaSuccess)
+        void *dev_view = nullptr;
+        if (cudaHostAlloc(reinterpret_cast<void **>(&w.pinned), sizeof(int), cudaHostAllocMapped) == cudaSuccess &&
+            cudaHostGetDevicePointer(&dev_view, w.pinned, 0) == cudaSuccess) {
             *w.pinned = 0;
-        else
+            w.pinned_dev = static_cast<int *>(dev_view);
+        } else {
             w.pinned = nullptr;
+        }
     }
     return w;
 }
@@ -297,9 +303,7 @@ void watch_this_call(int device, cudaStream_t stream) {
         return;
     }
     StatusWatch &w = status_watch(device);
-    const int *word = tvdcn_b200_device_status_address();
-    if (w.pinned != nullptr && word != nullptr)
-        (void)cudaMemcpyAsync(w.pinned, word, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    if (w.pinned != nullptr) (void)tvdcn_b200_publish_status(w.pinned_dev, stream);
 }
 
 Tensor make_workspace(size_t bytes, const Tensor &like) {
