@@ -391,6 +391,12 @@ class DeviceStep:
         self.engine = (self.L.tvdcn_b200_engine_name(pp, 0).decode(), self.L.tvdcn_b200_engine_name(pp, 1).decode())
         self.gw_ready = torch.cuda.Event()
         self.gw_ready.record()      # creates the underlying cudaEvent_t
+        import torch.distributed as dist
+        # only a step with an exchange asks for the "weight gradient ready" event (the call then puts the weight
+        # gradient first); a single GPU has nobody waiting for it
+        self.exchange = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+        self.copy_stream = torch.cuda.Stream(device, priority=-1)
+        self.gw_copied = torch.cuda.Event()
 
     def __call__(self):
         cfg, L, cabi = self.cfg, self.L, self.cabi
@@ -410,12 +416,20 @@ class DeviceStep:
                                                         vp(self.w), vp(self.off), vp(self.mask), vp(self.gx),
                                                         vp(self.gw), vp(self.goff), vp(self.gmask), vp(self.gb),
                                                         vp(self.ws), self.ws.numel(), st,
-                                                        ctypes.c_void_p(self.gw_ready.cuda_event)))
-        if self.gw16 is not None:
+                                                        ctypes.c_void_p(self.gw_ready.cuda_event)
+                                                        if self.exchange else None))
+        if self.gw16 is not None and self.exchange:
+            # 16-bit grad_weight goes into the f32 bucket on a stream of its own, behind the same event
+            self.copy_stream.wait_event(self.gw_ready)
+            with torch.cuda.stream(self.copy_stream):
+                self.bucket.weight_view.copy_(self.gw16)
+                self.gw_copied.record(self.copy_stream)
+            self.bucket.all_reduce_async(after=self.gw_copied)
+        elif self.gw16 is not None:
             self.bucket.weight_view.copy_(self.gw16)
             self.bucket.all_reduce_async()
         else:
-            self.bucket.all_reduce_async(after=self.gw_ready)
+            self.bucket.all_reduce_async(after=self.gw_ready if self.exchange else None)
         if cfg.softmax_mask:
             cabi.check(L.tvdcn_b200_mask_softmax_backward(cabi.F32, b, cfg.mask_groups, cfg.taps, sp, vp(self.gmask),
                                                           vp(self.mask), vp(self.glogits), st))
@@ -793,7 +807,10 @@ def main():
     torch.cuda.set_device(local)
     device = torch.device('cuda', local)
     if world > 1:
-        dist.init_process_group('nccl', device_id=device)
+        # the exchange's kernel needs only a few SMs, but needs them while the scatter kernel holds them all: on a
+        # high-priority stream its CTAs go first whenever an SM frees up
+        dist.init_process_group('nccl', device_id=device,
+                                pg_options=dist.ProcessGroupNCCL.Options(is_high_priority_stream=True))
     barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
 
     # Strong scaling: every rank generates the same global batch (CPU generator, seed 1000 + config) and keeps its

@@ -42,6 +42,10 @@ class GradBucket:
 
     ``weight_view`` / ``bias_view`` alias the buffer, so kernels can write their gradients straight into
     it (they are passed as the grad_weight / grad_bias pointers of the backward entry point).
+
+    For the exchange to run under the rest of the backward pass, create the NCCL process group with
+    ``pg_options=ProcessGroupNCCL.Options(is_high_priority_stream=True)``: the scatter kernel occupies every SM,
+    and a collective kernel of normal priority only gets SMs in that kernel's last wave.
     """
 
     def __init__(self, weight_shape, bias_elems: int, dtype=torch.float32, device='cpu', group=None):
