@@ -225,19 +225,30 @@ static cudaError_t run_gemm_scatter_tc(const tvdcn_problem *p, const GeoHost &g,
     return e;
 }
 
-// sampled weight gradient on the tensor cores; `gw_acc` is zero-initialised f32
+// sampled weight gradient on the tensor cores; `gw_acc` is zero-initialised f32.  `dense_channel_sum` (f32, Cd
+// values, may be NULL): wanted sum of the dense tensor over batch and space -- where the dense tensor is split into
+// bf16 parts anyway (f32 data) the same pass takes it and `*summed` says so, else the caller runs channel_sum.
 static cudaError_t run_sample_wgrad_tc(const tvdcn_problem *p, const GeoHost &g, const Plan &pl, const void *dense,
                                        const void *img, const void *offset, const void *mask, void *gw_acc, char *ws,
-                                       cudaStream_t stream) {
+                                       cudaStream_t stream, float *dense_channel_sum = nullptr,
+                                       bool *summed = nullptr) {
     const int mode = tc_mode_of(p->dtype);
     int *status = device_status_word();
     if (status == nullptr) return cudaErrorInvalidDevice;
     cudaError_t e = stage_image(p, g, pl, img, ws, stream);
     if (e != cudaSuccess) return e;
     const void *d_hi = dense, *d_lo = nullptr;
+    if (summed) *summed = false;
     if (p->dtype == TVDCN_F32) {
-        e = launch_split_f32((const float *)dense, ws + pl.dense_hi, ws + pl.dense_lo, (int64_t)g.B * g.Cd * g.P,
-                                 stream);
+        if (dense_channel_sum != nullptr &&
+            can_split_f32_with_channel_sum((const float *)dense, ws + pl.dense_hi, ws + pl.dense_lo, g.P)) {
+            e = launch_split_f32_channel_sum((const float *)dense, ws + pl.dense_hi, ws + pl.dense_lo, g.B, g.Cd, g.P,
+                                             dense_channel_sum, stream);
+            if (summed) *summed = true;
+        } else {
+            e = launch_split_f32((const float *)dense, ws + pl.dense_hi, ws + pl.dense_lo,
+                                 (int64_t)g.B * g.Cd * g.P, stream);
+        }
         if (e != cudaSuccess) return e;
         d_hi = ws + pl.dense_hi;
         d_lo = ws + pl.dense_lo;
@@ -479,8 +490,11 @@ int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_
     const bool tc_sw = pl.tc_sw && (p->dtype == TVDCN_F32 || (reinterpret_cast<uintptr_t>(dense_for_w) & 15) == 0);
 
     // the tensor-core weight-gradient kernel accumulates in a staged layout: convert right behind it
+    // (for conv with f32 data and f32 bias the split of grad_output also takes grad_bias)
+    bool bias_summed = false;
     auto wgrad_tc = [&](const void *dense, const void *img, cudaStream_t st) -> cudaError_t {
-        cudaError_t e = run_sample_wgrad_tc(p, g, pl, dense, img, offset, mask, gw_acc, ws, st);
+        float *sum_out = (!p->transposed && grad_bias != nullptr && aux == TVDCN_F32) ? (float *)grad_bias : nullptr;
+        cudaError_t e = run_sample_wgrad_tc(p, g, pl, dense, img, offset, mask, gw_acc, ws, st, sum_out, &bias_summed);
         if (e != cudaSuccess) return e;
         return launch_unpack_weight_grad((const float *)gw_acc, grad_weight, dt, g.groups, g.Cd / g.groups,
                                          g.Cs / g.groups, g.K, st);
@@ -501,7 +515,8 @@ int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_
         void *gi_acc = grad_input ? (pl.img_acc != NO_BUF ? (void *)(ws + pl.img_acc) : grad_input) : nullptr;
         if (side != nullptr) {
             CUDA_TRY(wgrad_tc(grad_output, input, wstream));
-            if (grad_bias) CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cd, g.P, grad_bias, wstream));
+            if (grad_bias && !bias_summed)
+                CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cd, g.P, grad_bias, wstream));
         }
         if (pl.tc_gs) {
             CUDA_TRY(run_gemm_scatter_tc(p, g, pl, grad_output, weight, offset, mask, input, grad_input, nullptr,
@@ -519,7 +534,7 @@ int tvdcn_b200_deform_conv_backward_ex(const tvdcn_problem *p, const void *grad_
             CUDA_TRY(wgrad_tc(grad_output, input, stream));
         else if (gw_acc)
             CUDA_TRY(launch_sample_wgrad(g, dt, aux, grad_output, input, offset, mask, gw_acc, stream));
-        if (grad_bias && side == nullptr)
+        if (grad_bias && side == nullptr && !bias_summed)
             CUDA_TRY(launch_channel_sum(dt, aux, grad_output, g.B, g.Cd, g.P, grad_bias, stream));
         if (gi_acc && pl.img_acc != NO_BUF) CUDA_TRY(launch_cast_from_acc(dt, gi_acc, grad_input, n_img, stream));
     } else {

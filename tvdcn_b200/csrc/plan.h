@@ -67,6 +67,11 @@ cudaError_t launch_pack_weight_kd(const void *w, int dtype, int mode, int groups
 cudaError_t launch_unpack_weight_grad(const float *staged, void *gw, int dtype, int groups, int cdg, int csg, int K,
                                       cudaStream_t stream);
 cudaError_t launch_split_f32(const float *src, void *hi, void *lo, int64_t n, cudaStream_t stream);
+// the same split of a [B, C, S] tensor plus sum_out[c] = sum over batch and space, in one pass; only where
+// can_split_f32_with_channel_sum says so (S a multiple of 4, pointers aligned for 16- / 8-byte accesses)
+bool can_split_f32_with_channel_sum(const float *src, const void *hi, const void *lo, int S);
+cudaError_t launch_split_f32_channel_sum(const float *src, void *hi, void *lo, int B, int C, int S, float *sum_out,
+                                         cudaStream_t stream);
 cudaError_t launch_to_channels_last(const void *src, void *dst, int B, int C, int S, int elem_bytes,
                                     cudaStream_t stream);
 cudaError_t launch_pack_weight_ks(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,

@@ -83,6 +83,47 @@ __global__ void __launch_bounds__(256) from_channels_last_bias_kernel(const floa
     }
 }
 
+// f32 [B, C, S] -> bf16 hi + lo (same layout) and, in the same pass, out[c] = sum over batch and space: one
+// 1024-thread block per channel, warp w walks the images b = w, w + 32, ...; S is a multiple of 4 and the three
+// pointers allow 16- / 8-byte accesses.  The sum is taken in a fixed order (no atomics).
+__global__ void __launch_bounds__(1024) split_f32_channel_sum_kernel(const float *__restrict__ src,
+                                                                     uint2 *__restrict__ hi, uint2 *__restrict__ lo,
+                                                                     int B, int C, int S, float *__restrict__ out) {
+    __shared__ float red[32];
+    const int c = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int s4 = S / 4;
+    float sum = 0.f;
+    for (int b = warp; b < B; b += 32) {
+        const int64_t row = ((int64_t)b * C + c) * (int64_t)s4;
+        const float4 *in = reinterpret_cast<const float4 *>(src) + row;
+        for (int i = lane; i < s4; i += 32) {
+            const float4 v = __ldg(in + i);
+            const float f[4] = {v.x, v.y, v.z, v.w};
+            uint32_t h[4], l[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const __nv_bfloat16 hb = __float2bfloat16_rn(f[k]);
+                h[k] = __bfloat16_as_ushort(hb);
+                l[k] = __bfloat16_as_ushort(__float2bfloat16_rn(f[k] - __bfloat162float(hb)));
+                sum += f[k];
+            }
+            hi[row + i] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+            lo[row + i] = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (warp == 0) {
+        float v = red[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) out[c] = v;
+    }
+}
+
 }  // namespace
 
 cudaError_t launch_from_channels_last_bias(const float *src, const float *bias, void *dst, int dst_dtype, int B, int C,
@@ -106,6 +147,19 @@ cudaError_t launch_from_channels_last_bias(const float *src, const float *bias, 
         from_channels_last_bias_kernel<__half><<<grid, 256, 0, stream>>>(src, bias, (__half *)dst, C, S);
     else
         return cudaErrorInvalidValue;
+    return cudaGetLastError();
+}
+
+bool can_split_f32_with_channel_sum(const float *src, const void *hi, const void *lo, int S) {
+    return S % 4 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+           ((reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(lo)) & 7) == 0;
+}
+
+cudaError_t launch_split_f32_channel_sum(const float *src, void *hi, void *lo, int B, int C, int S, float *sum_out,
+                                         cudaStream_t stream) {
+    if (B <= 0 || C <= 0 || S <= 0) return cudaSuccess;
+    LaunchScope scope("split_f32_channel_sum", stream);
+    split_f32_channel_sum_kernel<<<C, 1024, 0, stream>>>(src, (uint2 *)hi, (uint2 *)lo, B, C, S, sum_out);
     return cudaGetLastError();
 }
 
