@@ -192,3 +192,25 @@ def test_misaligned_16bit_grad_output_still_computes():
     assert names.get('sample_wgrad', 0) == 1 and 'dcn_wgrad_tc' not in names, names
     assert names.get('dcn_dgrad_tc', 0) == 1, names
     cases.assert_parity(got, ref, 2e-2, case.name)
+
+
+@pytest.mark.parametrize('shift', [0, 1], ids=['aligned', 'off_16_bytes'])
+def test_f32_bias_gradient_comes_from_the_split_pass(shift):
+    """f32 data, conv: grad_bias is taken in the pass that splits grad_output into bf16 parts (no channel_sum
+    launch) when grad_output allows 16-byte loads; a grad_output that starts 4 bytes off such a boundary takes the
+    plain split and the separate sum.  Both must match the oracle."""
+    case = Case('bias_in_split', 2, False, 3, 64, 64, (8, 8), (3, 3), (1, 1), (1, 1), (1, 1), (), 1, 1, 1, True, 1.0)
+    x, w, off, mask, bias, go = make_inputs(case, seed=53)
+    dev = [x.float().cuda(), w.float().cuda(), off.float().cuda(), mask.float().cuda(), bias.float().cuda()]
+    base = torch.empty(go.numel() + 4, dtype=torch.float32, device='cuda')
+    go_dev = base[shift:shift + go.numel()].view(go.shape)
+    go_dev.copy_(go.float())
+    assert go_dev.is_contiguous() and (go_dev.data_ptr() % 16 != 0) == bool(shift)
+    ref = run_oracle(case, *(t.double().cpu() for t in dev), go.double())
+    names, got = kernels_launched(lambda: cases.run_cabi(case, *dev, go_dev))
+    assert names.get('dcn_wgrad_tc', 0) == 1, names
+    if shift:
+        assert names.get('split_f32', 0) == 1 and names.get('channel_sum', 0) == 1, names
+    else:
+        assert names.get('split_f32_channel_sum', 0) == 1 and 'channel_sum' not in names, names
+    cases.assert_parity(got, ref, 1e-4, case.name)
