@@ -31,6 +31,7 @@ const char *tc_common(const tvdcn_problem *p, const GeoHost &g) {
     if (g.mg > 0 && (g.Cs / g.mg) % 64 != 0) return "channels per mask group must be a multiple of 64";
     if (((long long)g.B * g.S + 1) * g.Cs >= (1LL << 31) || (long long)g.B * g.P >= (1LL << 31))
         return "sampled image has 2^31 elements or more (32-bit element offsets)";
+    if ((long long)g.Cd * csg * g.K >= (1LL << 31)) return "weight has 2^31 elements or more (32-bit packing indices)";
     return nullptr;
 }
 

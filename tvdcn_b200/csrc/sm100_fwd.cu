@@ -510,23 +510,26 @@ __global__ void __launch_bounds__(256) to_channels_last32_kernel(const uint32_t 
 }
 
 // weight [Cd, csg, K] -> hi/lo [g][tap][d'][s'] (KS = true) or [g][tap][s'][d'] (KS = false)
+// (the weight tensor has fewer than 2^31 elements, checked by the launcher: 32-bit index arithmetic, whose
+// divisions by run-time values cost a quarter of the 64-bit ones this small kernel used to spend its time on)
 template <typename TW, bool KS>
 __global__ void pack_weight_kernel(const TW *__restrict__ w, int mode, int groups, int cdg, int csg, int K,
                                    uint16_t *__restrict__ hi, uint16_t *__restrict__ lo) {
-    const int64_t n = (int64_t)groups * K * cdg * csg;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        int64_t r = i;
-        int dl, sl;
+    const uint32_t n = (uint32_t)groups * (uint32_t)K * (uint32_t)cdg * (uint32_t)csg;
+    const uint32_t ucdg = (uint32_t)cdg, ucsg = (uint32_t)csg, uK = (uint32_t)K;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        uint32_t r = i;
+        uint32_t dl, sl;
         if (KS) {
-            sl = (int)(r % csg); r /= csg;
-            dl = (int)(r % cdg); r /= cdg;
+            sl = r % ucsg; r /= ucsg;
+            dl = r % ucdg; r /= ucdg;
         } else {
-            dl = (int)(r % cdg); r /= cdg;
-            sl = (int)(r % csg); r /= csg;
+            dl = r % ucdg; r /= ucdg;
+            sl = r % ucsg; r /= ucsg;
         }
-        const int tap = (int)(r % K);
-        const int grp = (int)(r / K);
-        const float v = to_acc(w[((int64_t)(grp * cdg + dl) * csg + sl) * K + tap]);
+        const uint32_t tap = r % uK;
+        const uint32_t grp = r / uK;
+        const float v = to_acc(w[((grp * ucdg + dl) * ucsg + sl) * uK + tap]);
         if (mode == TC_F16) {
             const __half h = __float2half_rn(v);
             hi[i] = *reinterpret_cast<const uint16_t *>(&h);
@@ -563,7 +566,8 @@ template <bool KS>
 cudaError_t launch_pack_weight(const void *w, int dtype, int mode, int groups, int cdg, int csg, int K, void *hi,
                                void *lo, cudaStream_t stream) {
     const int64_t n = (int64_t)groups * K * cdg * csg;
-    const int blocks = (int)std::min<int64_t>((n + 255) / 256, 148 * 8);
+    if (n >= ((int64_t)1 << 31)) return cudaErrorInvalidValue;
+    const int blocks = (int)std::min<int64_t>((n + 255) / 256, 148 * 16);
     LaunchScope scope("pack_weight", stream);
     if (dtype == DT_F32)
         pack_weight_kernel<float, KS><<<blocks, 256, 0, stream>>>((const float *)w, mode, groups, cdg, csg, K,
